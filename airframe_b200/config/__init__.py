@@ -4,15 +4,17 @@ from .base import (ConfigError, KeyReader, LayerSpec, ModelConfig, ModelSpec, Pa
 from .banitar import BanitarConfig
 from .fiferax import FiferaxConfig
 from .gemma2 import Gemma2Config
+from .zatasun import ZatasunConfig
 from .registry import (architecture_name, config_from_dict, config_from_folder,
                        known_architectures, register_architecture)
 
 register_architecture(Gemma2Config.architecture, Gemma2Config)
 register_architecture(FiferaxConfig.architecture, FiferaxConfig)
 register_architecture(BanitarConfig.architecture, BanitarConfig)
+register_architecture(ZatasunConfig.architecture, ZatasunConfig)
 
 __all__ = [
     "ConfigError", "KeyReader", "LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry",
-    "read_config_json", "BanitarConfig", "FiferaxConfig", "Gemma2Config", "architecture_name", "config_from_dict",
+    "read_config_json", "BanitarConfig", "FiferaxConfig", "Gemma2Config", "ZatasunConfig", "architecture_name", "config_from_dict",
     "config_from_folder", "known_architectures", "register_architecture",
 ]

@@ -1,5 +1,5 @@
 """Named configurations for the random-weights mode: the two tiny test
-models, the layer sizes of the released Gemma-2 models, a small Fiferax and a small Banitar, as
+models, the layer sizes of the released Gemma-2 models, a small Fiferax, a small Banitar and a small Zatasun, as
 config.json dictionaries.  Nothing here is read by the model code: a configuration always
 reaches it through ``config_from_dict``."""
 from __future__ import annotations
@@ -66,6 +66,23 @@ def _banitar_small() -> dict:
 
 
 PRESETS["banitar-small"] = _banitar_small()
+
+
+def _zatasun_small() -> dict:
+    """Zatasun with four layers, dense and routed feed-forwards in turn (sizes of no released model)."""
+    mixer = {"left": {"heads": 8, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.125,
+                      "rot": {"base": 10000.0, "dims": 64,
+                              "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}},
+             "left_scale": 1.0, "right": {"width": 512, "blocks": 4, "conv": 4}, "right_scale": 1.0}
+    moe = {"kind": "moe", "expert": {"ff": 256, "limit": 7.0}, "router": {"experts": 8, "top": 2},
+           "shared": {"ff": 512, "limit": 7.0}}
+    layers = [{"type": "parallel", "mixer": mixer, "mlp": {"kind": "dense", "ff": 1536} if i % 2 == 0 else moe}
+              for i in range(4)]
+    return {"architecture": "Zatasun", "vocab": 8192, "width": 512, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "layers": layers}
+
+
+PRESETS["zatasun-small"] = _zatasun_small()
 
 
 def preset(name: str) -> dict:

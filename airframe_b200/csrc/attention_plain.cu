@@ -625,49 +625,46 @@ AF_EXPORT int af_head_gate(void* x, long long x_stride, int dtype, const float* 
 // the packed row and the cache.  `pitch` > 0 (>= hd and >= dv): the heads of the packed row and the rows of the
 // cache are that many elements apart, zeros behind a head's own (a mixer pads its heads up to a size that the
 // tensor-core attention kernels take); 0: q and k heads hd apart, v heads dv apart.
+// Where a k head's row of token t goes in the cache (nullptr: nowhere).
 template <typename T>
-__global__ void __launch_bounds__(128)
-qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float* __restrict__ proj, long long ld,
-                          const float* __restrict__ bias, const float* __restrict__ q_weight,
-                          const float* __restrict__ k_weight, float eps, int norm_after, float magnitude,
-                          int v_from_k, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                          const int* __restrict__ slots, const int* __restrict__ len_after,
-                          const float* __restrict__ inv_freq, int n_tokens, int nq, int nkv, int hd, int dv, int rot_dim,
-                          int pairing, T* __restrict__ kcache, T* __restrict__ vcache,
-                          const int* __restrict__ page_table, int max_pages, int ring_rows, int pitch) {
-  pdl_launch_dependents();
-  const int lane = threadIdx.x & 31;
-  const long long wi = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (wi >= (long long)n_tokens * (nq + nkv)) return;
-  const int t = (int)(wi / (nq + nkv)), head = (int)(wi % (nq + nkv));
-  const bool is_k = head >= nq;
-  const int pos = positions[t];
-  const int pk = pitch > 0 ? pitch : hd, pv = pitch > 0 ? pitch : dv;      // elements between heads (and of a cache row)
-  // where a k head's row goes in the cache
-  T *kdst = nullptr, *vdst = nullptr;
-  if (kcache != nullptr && is_k) {
-    const int seq = seq_of_token[t];
-    const int slot = slots[seq];
-    if (slot >= 0 && !(ring_rows > 0 && pos + ring_rows < len_after[seq])) {
-      const int r = ring_rows > 0 ? pos % ring_rows : pos;
-      if (AF_INDEX_OK(pos >= 0 && r / AF_PAGE < max_pages, r)) {
-        const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
-        if (AF_INDEX_OK(page >= 0, page)) {
-          const size_t at = ((size_t)page * nkv + (head - nq)) * AF_PAGE + r % AF_PAGE;
-          kdst = kcache + at * pk;
-          vdst = vcache + at * pv;
-        }
+__device__ __forceinline__ void qk_cache_rows(T* kcache, T* vcache, const int* __restrict__ seq_of_token,
+                                              const int* __restrict__ slots, const int* __restrict__ len_after,
+                                              const int* __restrict__ page_table, int max_pages, int ring_rows, int nkv,
+                                              int t, int pos, int g, int pk, int pv, T** kdst, T** vdst) {
+  *kdst = nullptr, *vdst = nullptr;
+  if (kcache == nullptr) return;
+  const int seq = seq_of_token[t];
+  const int slot = slots[seq];
+  if (slot >= 0 && !(ring_rows > 0 && pos + ring_rows < len_after[seq])) {
+    const int r = ring_rows > 0 ? pos % ring_rows : pos;
+    if (AF_INDEX_OK(pos >= 0 && r / AF_PAGE < max_pages, r)) {
+      const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
+      if (AF_INDEX_OK(page >= 0, page)) {
+        const size_t at = ((size_t)page * nkv + g) * AF_PAGE + r % AF_PAGE;
+        *kdst = kcache + at * pk;
+        *vdst = vcache + at * pv;
       }
     }
   }
-  pdl_wait();
+}
+
+// One q or k head of one token, by one warp: norm (per head with the weight `w` of hd values, or with the factor
+// `inv_whole` that the caller took over the whole projection and a weight that holds this head's own hd values),
+// rotation, the norm behind it, packing, the cache row, and a k head's value head.
+template <typename T>
+__device__ __forceinline__ void qk_pack_head(T* __restrict__ qkv, long long out_stride, const float* __restrict__ proj,
+                                             long long ld, const float* __restrict__ bias, const float* __restrict__ w,
+                                             bool whole, float inv_whole, float eps, int norm_after, float magnitude,
+                                             int v_from_k, const float* __restrict__ inv_freq, int nq, int nkv, int hd,
+                                             int dv, int rot_dim, int pairing, int pk, int pv, int t, int head, int pos,
+                                             int lane, T* kdst, T* vdst) {
+  const bool is_k = head >= nq;
   const float* x = proj + (size_t)t * ld + (size_t)head * hd;
   const float* xb = bias ? bias + (size_t)head * hd : nullptr;
-  const float* w = is_k ? k_weight : q_weight;
   T* orow = qkv + (size_t)t * out_stride;
   T* dst = orow + (size_t)head * pk;                        // q heads and k heads keep their places
-  float inv = 1.f;
-  if (w != nullptr) {
+  float inv = whole ? inv_whole : 1.f;
+  if (w != nullptr && !whole) {
     float ss = 0.f;
     for (int i = lane; i < hd; i += 32) {
       const float v = x[i] + (xb ? xb[i] : 0.f);
@@ -728,15 +725,83 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float* __restrict__ proj, long long ld,
+                          const float* __restrict__ bias, const float* __restrict__ q_weight,
+                          const float* __restrict__ k_weight, float eps, int norm_after, float magnitude,
+                          int v_from_k, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                          const int* __restrict__ slots, const int* __restrict__ len_after,
+                          const float* __restrict__ inv_freq, int n_tokens, int nq, int nkv, int hd, int dv, int rot_dim,
+                          int pairing, T* __restrict__ kcache, T* __restrict__ vcache,
+                          const int* __restrict__ page_table, int max_pages, int ring_rows, int pitch) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const long long wi = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wi >= (long long)n_tokens * (nq + nkv)) return;
+  const int t = (int)(wi / (nq + nkv)), head = (int)(wi % (nq + nkv));
+  const int pos = positions[t];
+  const int pk = pitch > 0 ? pitch : hd, pv = pitch > 0 ? pitch : dv;      // elements between heads (and of a cache row)
+  T *kdst = nullptr, *vdst = nullptr;
+  if (head >= nq)
+    qk_cache_rows(kcache, vcache, seq_of_token, slots, len_after, page_table, max_pages, ring_rows, nkv, t, pos,
+                  head - nq, pk, pv, &kdst, &vdst);
+  pdl_wait();
+  qk_pack_head(qkv, out_stride, proj, ld, bias, head >= nq ? k_weight : q_weight, false, 1.f, eps, norm_after, magnitude,
+               v_from_k, inv_freq, nq, nkv, hd, dv, rot_dim, pairing, pk, pv, t, head, pos, lane, kdst, vdst);
+}
+
+// The same with q (and k) normed over the whole projection of the token, all heads at once: the weights hold
+// nq * hd and nkv * hd values.  One block per token: the two mean squares first, then a warp per head in turn.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_whole_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float* __restrict__ proj, long long ld,
+                                const float* __restrict__ bias, const float* __restrict__ q_weight,
+                                const float* __restrict__ k_weight, float eps, int norm_after, float magnitude,
+                                int v_from_k, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                const int* __restrict__ slots, const int* __restrict__ len_after,
+                                const float* __restrict__ inv_freq, int nq, int nkv, int hd, int dv, int rot_dim,
+                                int pairing, T* __restrict__ kcache, T* __restrict__ vcache,
+                                const int* __restrict__ page_table, int max_pages, int ring_rows, int pitch) {
+  pdl_launch_dependents();
+  __shared__ float scratch[33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int pk = pitch > 0 ? pitch : hd, pv = pitch > 0 ? pitch : dv;
+  pdl_wait();
+  const float* row = proj + (size_t)t * ld;
+  const int n_q = nq * hd, n_k = nkv * hd;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < n_q + n_k; i += blockDim.x) {
+    const float v = row[i] + (bias ? bias[i] : 0.f);
+    if (i < n_q) sq += v * v; else sk += v * v;
+  }
+  sq = block_sum(sq, scratch);
+  sk = block_sum(sk, scratch);
+  const float inv_q = rsqrtf(sq / (float)n_q + eps), inv_k = rsqrtf(sk / (float)n_k + eps);
+  for (int head = warp; head < nq + nkv; head += nwarp) {
+    const bool is_k = head >= nq;
+    T *kdst = nullptr, *vdst = nullptr;
+    if (is_k)
+      qk_cache_rows(kcache, vcache, seq_of_token, slots, len_after, page_table, max_pages, ring_rows, nkv, t, pos,
+                    head - nq, pk, pv, &kdst, &vdst);
+    const float* w = is_k ? k_weight + (size_t)(head - nq) * hd : q_weight + (size_t)head * hd;
+    qk_pack_head(qkv, out_stride, proj, ld, bias, w, true, is_k ? inv_k : inv_q, eps, norm_after, magnitude, v_from_k,
+                 inv_freq, nq, nkv, hd, dv, rot_dim, pairing, pk, pv, t, head, pos, lane, kdst, vdst);
+  }
+}
+
 AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, const float* proj, long long ld,
                                     const float* bias, const float* q_weight, const float* k_weight, float eps,
                                     int norm_after, float magnitude, int v_from_k,
                                     const int* positions, const int* seq_of_token, const int* slots,
                                     const int* len_after, const float* inv_freq, int n_tokens, int nq, int nkv, int hd,
                                     int dv, int rot_dim, int pairing, void* kcache, void* vcache, const int* page_table,
-                                    int max_pages, int ring_rows, int pitch, cudaStream_t stream) {
+                                    int max_pages, int ring_rows, int pitch, int whole_norm, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   AF_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && hd > 0 && dv > 0, "af_qk_norm_rope_store: bad sizes");
+  AF_REQUIRE(!whole_norm || q_weight != nullptr, "af_qk_norm_rope_store: a norm over the whole projection needs its weights");
   AF_REQUIRE(pitch == 0 || (pitch >= hd && pitch >= dv), "af_qk_norm_rope_store: pitch %d below the heads' sizes", pitch);
 
   AF_REQUIRE(!v_from_k || dv == hd, "af_qk_norm_rope_store: values that are the keys have their size");
@@ -746,6 +811,14 @@ AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, 
   AF_REQUIRE(ring_rows % AF_PAGE == 0, "af_qk_norm_rope_store: ring rows %d not whole pages", ring_rows);
   AF_REQUIRE((kcache == nullptr) == (vcache == nullptr), "af_qk_norm_rope_store: k and v cache");
   AF_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "af_qk_norm_rope_store: both norm weights or none");
+  if (whole_norm) {
+    AF_DISPATCH_DTYPE(dtype, T,
+                      af_launch(qk_whole_norm_rope_store_kernel<T>, dim3((unsigned)n_tokens), dim3(256), 0, stream, (T*)qkv,
+                                out_stride, proj, ld, bias, q_weight, k_weight, eps, norm_after, magnitude, v_from_k,
+                                positions, seq_of_token, slots, len_after, inv_freq, nq, nkv, hd, dv, rot_dim, pairing,
+                                (T*)kcache, (T*)vcache, page_table, max_pages, ring_rows, pitch));
+    AF_CHECK_LAUNCH("af_qk_norm_rope_store");
+  }
   const long long warps = (long long)n_tokens * (nq + nkv);
   const long long blocks = (warps + 3) / 4;
   AF_REQUIRE(blocks < (1ll << 31), "af_qk_norm_rope_store: too many rows");

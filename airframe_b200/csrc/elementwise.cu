@@ -626,3 +626,113 @@ AF_EXPORT int af_add_scaled_rmsnorm(float* x, const void* a, int a_dtype, int a_
                               hidden, eps, offset));
   AF_CHECK_LAUNCH("af_add_scaled_rmsnorm");
 }
+
+// ---------------------------------------------------------------- a norm on a sublayer's output
+
+// x += norm(s_a a + s_b b) (offset + w_post), the sum and the norm's statistics in 32 bits (terms as in
+// add_scaled_rmsnorm: a tensor of the compute dtype or float partial sums, added in index order).  Then, when y is
+// given: y = norm(x) (offset_next + w_next) with eps_next, or with no w_next the new x itself in y's dtype (what a
+// sublayer that reads the stream as it stands is given).  One block per row; the sum stays in shared memory
+// between the passes.
+template <typename TY>
+__global__ void __launch_bounds__(256)
+add_normed_terms_kernel(float* __restrict__ x, const void* __restrict__ a, int a_dtype, int a_parts, float scale_a,
+                        const void* __restrict__ b, int b_dtype, int b_parts, float scale_b, size_t part_stride,
+                        const float* __restrict__ w_post, float eps_post, float offset_post, TY* __restrict__ y,
+                        const float* __restrict__ w_next, float eps_next, float offset_next, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  float* xr = x + (size_t)r * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const size_t at = (size_t)r * hidden + i;
+    float t = scale_a * term_value(a, a_dtype, a_parts, part_stride, at);
+    if (b != nullptr) t += scale_b * term_value(b, b_dtype, b_parts, part_stride, at);
+    row[i] = t;
+    ss += t * t;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps_post);
+  float s2 = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = xr[i] + row[i] * inv * (offset_post + w_post[i]);
+    xr[i] = v;
+    row[i] = v;
+    s2 += v * v;
+  }
+  if (y == nullptr) return;
+  TY* yr = y + (size_t)r * hidden;
+  if (w_next == nullptr) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) yr[i] = from_f32<TY>(row[i]);
+    return;
+  }
+  s2 = block_sum(s2, scratch);
+  const float inv2 = rsqrtf(s2 / (float)hidden + eps_next);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) yr[i] = from_f32<TY>(row[i] * inv2 * (offset_next + w_next[i]));
+}
+
+AF_EXPORT int af_add_normed_terms(float* x, const void* a, int a_dtype, int a_parts, float scale_a, const void* b,
+                                  int b_dtype, int b_parts, float scale_b, const float* w_post, float eps_post,
+                                  float offset_post, void* y, int y_dtype, const float* w_next, float eps_next,
+                                  float offset_next, int n_rows, int hidden, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AF_REQUIRE(n_rows > 0 && hidden > 0 && a != nullptr && w_post != nullptr && a_parts >= 1 && b_parts >= 1,
+             "af_add_normed_terms: bad sizes");
+  AF_REQUIRE((a_dtype == AF_F32 || (a_dtype == AF_BF16 && a_parts == 1)) &&
+             (b == nullptr || b_dtype == AF_F32 || (b_dtype == AF_BF16 && b_parts == 1)),
+             "af_add_normed_terms: partial sums are float");
+  AF_REQUIRE((size_t)hidden * sizeof(float) <= 48 * 1024, "af_add_normed_terms: rows of up to 12288 values");
+  const size_t part_stride = (size_t)n_rows * hidden;
+  const int threads = hidden >= 2048 ? 256 : 128;
+  AF_DISPATCH_DTYPE(y_dtype, TY,
+                    af_launch(add_normed_terms_kernel<TY>, dim3(n_rows), dim3(threads), (size_t)hidden * sizeof(float),
+                              stream, x, a, a_dtype, a_parts, scale_a, b, b_dtype, b_parts, scale_b, part_stride, w_post,
+                              eps_post, offset_post, (TY*)y, w_next, eps_next, offset_next, hidden));
+  AF_CHECK_LAUNCH("af_add_normed_terms");
+}
+
+// y = x in y's dtype (of the listed rows when `rows` is given): what a sublayer that reads the residual stream as
+// it stands is given on the 16-bit path.
+template <typename TY>
+__global__ void cast_rows_kernel(TY* __restrict__ y, const float* __restrict__ x, const int* __restrict__ rows,
+                                 int hidden, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t r = i / hidden, c = i % hidden;
+  const size_t src = rows != nullptr ? (size_t)rows[r] : r;
+  y[i] = from_f32<TY>(x[src * hidden + c]);
+}
+
+AF_EXPORT int af_cast_rows(void* y, int y_dtype, const float* x, const int* rows, int n_rows, int hidden,
+                           cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AF_REQUIRE(n_rows > 0 && hidden > 0, "af_cast_rows: bad sizes");
+  const size_t total = (size_t)n_rows * hidden;
+  const size_t blocks = (total + 255) / 256;
+  AF_REQUIRE(blocks < (1ull << 31), "af_cast_rows: too many rows");
+  AF_DISPATCH_DTYPE(y_dtype, TY,
+                    af_launch(cast_rows_kernel<TY>, dim3((unsigned)blocks), dim3(256), 0, stream, (TY*)y, x, rows, hidden, total));
+  AF_CHECK_LAUNCH("af_cast_rows");
+}
+
+// z *= s
+__global__ void scale_kernel(float* __restrict__ z, size_t n, float s) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) z[i] *= s;
+}
+
+AF_EXPORT int af_scale(float* z, long long n, float s, cudaStream_t stream) {
+  if (n == 0) return 0;
+  AF_REQUIRE(n > 0 && z != nullptr, "af_scale: bad sizes");
+  const size_t blocks = ((size_t)n + 255) / 256;
+  AF_REQUIRE(blocks < (1ull << 31), "af_scale: too many values");
+  af_launch(scale_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, z, (size_t)n, s);
+  AF_CHECK_LAUNCH("af_scale");
+}

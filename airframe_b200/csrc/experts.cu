@@ -1,0 +1,242 @@
+// A routed feed-forward (mixture of experts) without a word read back by the host:
+//   expert_route   per token the router's logits in 32 bits, a score per expert (the sigmoid of its logit), the `top`
+//                  experts with the largest scores (equal scores: the lower index) and their scores; also the
+//                  sigmoid of one more row of the router matrix when there is one (the gate of a shared expert);
+//   expert_plan    the (token, choice) pairs sorted by expert: a permutation, and a table of tiles of up to 32
+//                  pairs of one expert each;
+//   expert_rows    a tile's rows times its expert's matrices on the CUDA cores, 32-bit sums in index order:
+//                  either gate and up with the activation behind them, or down.
+// The order of the pairs of an expert depends on the order in which blocks arrive, but every row of a tile is
+// worked out by itself, so no result depends on it.
+#include "common.cuh"
+
+#define AF_EX_TM 32
+#define AF_EX_TN 64
+#define AF_EX_TK 32
+
+// ---------------------------------------------------------------- the router
+
+template <typename TX>
+__global__ void __launch_bounds__(128)
+expert_route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ shared_gate,
+                    const TX* __restrict__ h, const float* __restrict__ router, int hidden, int n_experts, int top) {
+  pdl_launch_dependents();
+  extern __shared__ float score[];                  // n_experts (+ 1) scores
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int t = blockIdx.x;
+  const int rows = n_experts + (shared_gate != nullptr ? 1 : 0);
+  pdl_wait();
+  h = pdl_fresh(h);
+  const TX* x = h + (size_t)t * hidden;
+  for (int e = warp; e < rows; e += nwarp) {
+    const float* w = router + (size_t)e * hidden;
+    float z = 0.f;
+    for (int i = lane; i < hidden; i += 32) z = fmaf(w[i], to_f32<TX>(x[i]), z);
+    z = warp_sum(z);
+    if (lane == 0) score[e] = 1.f / (1.f + expf(-z));
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  if (shared_gate != nullptr && lane == 0) shared_gate[t] = score[n_experts];
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;                              // (a sigmoid is never negative; a chosen expert's score is set to -2)
+    int at = n_experts;
+    for (int e = lane; e < n_experts; e += 32)
+      if (score[e] > best) best = score[e], at = e; // (ascending e: the lower index wins among equals)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) best = ob, at = oa;
+    }
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = at;
+      wts[(size_t)t * top + k] = best;
+      score[at] = -2.f;
+    }
+    __syncwarp();
+  }
+}
+
+AF_EXPORT int af_expert_route(int* ids, float* wts, float* shared_gate, const void* h, int h_dtype, const float* router,
+                              int n_tokens, int hidden, int n_experts, int top, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && hidden > 0 && n_experts > 0 && top >= 1 && top <= n_experts,
+             "af_expert_route: %d of %d experts", top, n_experts);
+  AF_REQUIRE(n_experts <= 8192, "af_expert_route: up to 8192 experts");
+  const size_t smem = (size_t)(n_experts + 1) * sizeof(float);
+  AF_DISPATCH_DTYPE(h_dtype, TX,
+                    af_launch(expert_route_kernel<TX>, dim3(n_tokens), dim3(128), smem, stream, ids, wts, shared_gate,
+                              (const TX*)h, router, hidden, n_experts, top));
+  AF_CHECK_LAUNCH("af_expert_route");
+}
+
+// ---------------------------------------------------------------- pairs by expert
+
+// One block.  plan: [0] tiles in use; then per tile (expert, first sorted row, rows).  perm[sorted row] = pair.
+__global__ void __launch_bounds__(1024)
+expert_plan_kernel(int* __restrict__ perm, int* __restrict__ plan, const int* __restrict__ ids, int n_pairs,
+                   int n_experts, int max_tiles) {
+  pdl_launch_dependents();
+  extern __shared__ int sh[];                       // count[E], first[E], cursor[E]
+  int* count = sh;
+  int* first = sh + n_experts;
+  int* cursor = sh + 2 * n_experts;
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0, cursor[e] = 0;
+  __syncthreads();
+  pdl_wait();
+  ids = pdl_fresh(ids);
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (AF_INDEX_OK(e >= 0 && e < n_experts, e)) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int rows = 0, tiles = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      first[e] = rows;
+      for (int r = 0; r < count[e] && tiles < max_tiles; r += AF_EX_TM, ++tiles) {
+        plan[1 + 3 * tiles] = e;
+        plan[2 + 3 * tiles] = rows + r;
+        plan[3 + 3 * tiles] = min(AF_EX_TM, count[e] - r);
+      }
+      rows += count[e];
+    }
+    plan[0] = tiles;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < n_experts) perm[first[e] + atomicAdd(&cursor[e], 1)] = p;
+  }
+}
+
+AF_EXPORT int af_expert_plan(int* perm, int* plan, const int* ids, int n_pairs, int n_experts, int max_tiles,
+                             cudaStream_t stream) {
+  if (n_pairs == 0) return 0;
+  AF_REQUIRE(n_pairs > 0 && n_experts > 0 && n_experts <= 4096, "af_expert_plan: bad sizes");
+  // (every expert may end on a tile that is not full)
+  AF_REQUIRE(max_tiles >= n_pairs / AF_EX_TM + n_experts || max_tiles >= n_pairs,
+             "af_expert_plan: room for %d tiles is too little", max_tiles);
+  af_launch(expert_plan_kernel, dim3(1), dim3(1024), (size_t)3 * n_experts * sizeof(int), stream, perm, plan, ids,
+            n_pairs, n_experts, max_tiles);
+  AF_CHECK_LAUNCH("af_expert_plan");
+}
+
+// ---------------------------------------------------------------- a tile's rows times its expert's matrices
+
+// The activation of these experts: g = min(g, limit), u = clamp(u, -limit, limit), g sigmoid(1.702 g) (u + 1).
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+}
+
+// DUAL: out[sorted row][n] = act(s (x . w0[e][n]), s (x . w1[e][n])) * post, x the row of `a` that the pair's
+//       token names, s the pair's weight (a weight on an expert's input goes through its products, which have no
+//       bias), post the token's `scale_out` (1 without); out of the compute dtype, rows of N values.
+// else: out[(choice, token)][n] = a[sorted row] . w0[e][n] as floats: [top][tokens][N], partial sums that the
+//       residual kernel adds.
+// Without a plan (plan == nullptr) there is one expert and the rows are the tokens in order.
+template <typename T, bool DUAL>
+__global__ void __launch_bounds__(256)
+expert_rows_kernel(void* __restrict__ out_, const T* __restrict__ a, const T* __restrict__ w0, const T* __restrict__ w1,
+                   const int* __restrict__ perm, const int* __restrict__ plan, const float* __restrict__ pair_weight,
+                   const float* __restrict__ scale_out, int n_rows, int n_tokens, int top, int N, int K, float limit) {
+  pdl_launch_dependents();
+  __shared__ float as[AF_EX_TM][AF_EX_TK];
+  __shared__ float w0s[AF_EX_TN][AF_EX_TK + 1];
+  __shared__ float w1s[DUAL ? AF_EX_TN : 1][AF_EX_TK + 1];
+  __shared__ int src_row[AF_EX_TM];                 // the row of `a` a tile row reads (-1: none)
+  __shared__ int pair_of[AF_EX_TM];
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const int n0 = blockIdx.y * AF_EX_TN;
+  pdl_wait();
+  plan = pdl_fresh(plan);
+  perm = pdl_fresh(perm);
+  a = pdl_fresh(a);
+  int expert = 0, row0 = blockIdx.x * AF_EX_TM, rows = min(AF_EX_TM, n_rows - row0);
+  if (plan != nullptr) {
+    if ((int)blockIdx.x >= plan[0]) return;
+    expert = plan[1 + 3 * blockIdx.x], row0 = plan[2 + 3 * blockIdx.x], rows = plan[3 + 3 * blockIdx.x];
+  }
+  if (rows <= 0) return;
+  if (threadIdx.x < AF_EX_TM) {
+    const int m = threadIdx.x;
+    int pair = -1;
+    if (m < rows) pair = perm != nullptr ? perm[row0 + m] : row0 + m;
+    pair_of[m] = pair;
+    src_row[m] = pair < 0 ? -1 : (DUAL ? pair / top : row0 + m);
+  }
+  __syncthreads();
+  const T* w0e = w0 + (size_t)expert * N * K;
+  const T* w1e = DUAL ? w1 + (size_t)expert * N * K : nullptr;
+  float acc0[AF_EX_TM / 4], acc1[AF_EX_TM / 4];
+#pragma unroll
+  for (int m = 0; m < AF_EX_TM / 4; ++m) acc0[m] = acc1[m] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += AF_EX_TK) {
+    for (int e = threadIdx.x; e < AF_EX_TM * AF_EX_TK; e += 256) {
+      const int m = e / AF_EX_TK, k = e % AF_EX_TK;
+      const int r = src_row[m];
+      as[m][k] = (r >= 0 && k0 + k < K) ? to_f32<T>(a[(size_t)r * K + k0 + k]) : 0.f;
+    }
+    for (int e = threadIdx.x; e < AF_EX_TN * AF_EX_TK; e += 256) {
+      const int n = e / AF_EX_TK, k = e % AF_EX_TK;
+      const bool in = n0 + n < N && k0 + k < K;
+      w0s[n][k] = in ? to_f32<T>(w0e[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+      if (DUAL) w1s[n][k] = in ? to_f32<T>(w1e[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < AF_EX_TK; ++k) {
+      const float p = w0s[tx][k];
+      const float q = DUAL ? w1s[tx][k] : 0.f;
+#pragma unroll
+      for (int m = 0; m < AF_EX_TM / 4; ++m) {
+        const float v = as[ty + 4 * m][k];
+        acc0[m] = fmaf(p, v, acc0[m]);
+        if (DUAL) acc1[m] = fmaf(q, v, acc1[m]);
+      }
+    }
+    __syncthreads();
+  }
+  const int n = n0 + tx;
+  if (n >= N) return;
+#pragma unroll
+  for (int m = 0; m < AF_EX_TM / 4; ++m) {
+    const int row = ty + 4 * m;
+    const int pair = pair_of[row];
+    if (pair < 0) continue;
+    if (DUAL) {
+      const float s = pair_weight != nullptr ? pair_weight[pair] : 1.f;
+      const float post = scale_out != nullptr ? scale_out[pair / top] : 1.f;
+      static_cast<T*>(out_)[(size_t)(row0 + row) * N + n] = from_f32<T>(clamped_glu(s * acc0[m], s * acc1[m], limit) * post);
+    } else {
+      const int token = pair / top, choice = pair % top;
+      static_cast<float*>(out_)[((size_t)choice * n_tokens + token) * N + n] = acc0[m];
+    }
+  }
+}
+
+AF_EXPORT int af_expert_rows(void* out, const void* a, const void* w0, const void* w1, int dtype, const int* perm,
+                             const int* plan, const float* pair_weight, const float* scale_out, int n_rows,
+                             int n_tokens, int top, int max_tiles, int N, int K, float limit, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AF_REQUIRE(n_rows > 0 && n_tokens > 0 && top >= 1 && N > 0 && K > 0, "af_expert_rows: bad sizes");
+  AF_REQUIRE((plan == nullptr) == (perm == nullptr), "af_expert_rows: a plan and its permutation, or neither");
+  AF_REQUIRE(n_rows == n_tokens * top, "af_expert_rows: %d rows for %d tokens with %d choices", n_rows, n_tokens, top);
+  const int tiles = plan != nullptr ? max_tiles : (n_rows + AF_EX_TM - 1) / AF_EX_TM;
+  AF_REQUIRE(tiles > 0, "af_expert_rows: no tiles");
+  const dim3 grid(tiles, (N + AF_EX_TN - 1) / AF_EX_TN);
+  AF_REQUIRE(grid.y < 65536, "af_expert_rows: too many outputs");
+  if (w1 != nullptr) {
+    AF_DISPATCH_DTYPE(dtype, T,
+                      af_launch(expert_rows_kernel<T, true>, grid, dim3(256), 0, stream, out, (const T*)a, (const T*)w0,
+                                (const T*)w1, perm, plan, pair_weight, scale_out, n_rows, n_tokens, top, N, K, limit));
+  } else {
+    AF_DISPATCH_DTYPE(dtype, T,
+                      af_launch(expert_rows_kernel<T, false>, grid, dim3(256), 0, stream, out, (const T*)a, (const T*)w0,
+                                (const T*)nullptr, perm, plan, pair_weight, scale_out, n_rows, n_tokens, top, N, K, limit));
+  }
+  AF_CHECK_LAUNCH("af_expert_rows");
+}

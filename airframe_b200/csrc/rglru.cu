@@ -1,0 +1,241 @@
+// A gated linear recurrence over a vector state with a short causal convolution in front (the recurrent block
+// of Griffin: De et al., "Griffin: Mixing Gated Linear Recurrences with Local Attention for Efficient Language
+// Models"), in three kernels between the input and output products:
+//   conv_rows   u = conv(x + bx) + cb per channel over the tokens of each sequence, the tokens before the step
+//               taken from the sequence's state;
+//   gate_rows   r = sigmoid(Wa_b u_b + ba), i = sigmoid(Wi_b u_b + bi) with block-diagonal Wa, Wi (b = the
+//               block of channels), then a = exp(-c r softplus(lam)) and the token's input sqrt(1 - a^2) i u;
+//   decay_scan  S <- a S + input token after token, out = S * gelu_tanh(y + by), and the state left for the next
+//               step: S and the last taps - 1 inputs of the convolution.
+// Everything here is 32-bit: the rows come from products that accumulate in 32 bits, the weights of the gates are
+// read in the compute dtype and widened, and only the output (the input of the output product) is of the compute dtype.
+// The state of a sequence is float [taps][width]: row 0 is S, rows 1 .. taps-1 the convolution's last inputs, oldest first.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- the convolution
+
+__global__ void __launch_bounds__(256)
+conv_rows_kernel(float* __restrict__ u, const float* __restrict__ proj, long long ld, int off_x,
+                 const float* __restrict__ bx, const float* __restrict__ cw, const float* __restrict__ cb,
+                 const float* __restrict__ state, const int* __restrict__ seq_of_token,
+                 const int* __restrict__ seq_starts, const int* __restrict__ slots, int n_tokens, int width, int taps) {
+  pdl_launch_dependents();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_tokens * width) return;
+  const int t = (int)(i / width), c = (int)(i % width);
+  const int seq = seq_of_token[t];
+  const int first = seq_starts[seq];
+  const int slot = slots[seq];
+  const float xb = bx[c];
+  float acc = cb[c];
+  pdl_wait();
+  proj = pdl_fresh(proj);
+  state = pdl_fresh(state);
+  for (int k = 0; k < taps; ++k) {
+    const int src = t - (taps - 1 - k);             // the token this tap looks at (the last tap: the current one)
+    float v;
+    if (src >= first) {
+      v = proj[(size_t)src * ld + off_x + c] + xb;
+    } else {
+      // before the step: row 1 + (taps - 1) + (src - first) of the state (zeros for a sequence that just began)
+      v = slot >= 0 ? state[((size_t)slot * taps + (taps + src - first)) * width + c] : 0.f;
+    }
+    acc += cw[(size_t)c * taps + k] * v;
+  }
+  u[i] = acc;
+}
+
+AF_EXPORT int af_conv_rows(float* u, const float* proj, long long ld, int off_x, const float* bx, const float* cw,
+                           const float* cb, const float* state, const int* seq_of_token, const int* seq_starts,
+                           const int* slots, int n_tokens, int width, int taps, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && width > 0 && taps >= 1, "af_conv_rows: bad sizes");
+  const size_t blocks = ((size_t)n_tokens * width + 255) / 256;
+  AF_REQUIRE(blocks < (1ull << 31), "af_conv_rows: too many rows");
+  af_launch(conv_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, u, proj, ld, off_x, bx, cw, cb, state,
+            seq_of_token, seq_starts, slots, n_tokens, width, taps);
+  AF_CHECK_LAUNCH("af_conv_rows");
+}
+
+// ---------------------------------------------------------------- the gates
+
+// A block owns 32 tokens, one block of channels and 64 of its outputs, for both gates; thread (tx, ty) owns
+// output tx for the tokens ty, ty + 4, ...  Every output adds its products in index order, whatever else is in
+// the step.  Wa, Wi: [blocks][out][in] of the compute dtype.
+#define AF_GR_TM 32
+#define AF_GR_TN 64
+#define AF_GR_TK 32
+template <typename TW>
+__global__ void __launch_bounds__(256)
+gate_rows_kernel(float* __restrict__ decay, float* __restrict__ input, const float* __restrict__ u,
+                 const TW* __restrict__ wa, const TW* __restrict__ wi, const float* __restrict__ ba,
+                 const float* __restrict__ bi, const float* __restrict__ rate, int n_tokens, int width, int bw) {
+  pdl_launch_dependents();
+  __shared__ float us[AF_GR_TM][AF_GR_TK];
+  __shared__ float was[AF_GR_TN][AF_GR_TK + 1];
+  __shared__ float wis[AF_GR_TN][AF_GR_TK + 1];
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const int t0 = blockIdx.x * AF_GR_TM, b = blockIdx.y, n0 = blockIdx.z * AF_GR_TN;
+  const TW* wab = wa + (size_t)b * bw * bw;
+  const TW* wib = wi + (size_t)b * bw * bw;
+  float acc_a[AF_GR_TM / 4], acc_i[AF_GR_TM / 4];
+#pragma unroll
+  for (int m = 0; m < AF_GR_TM / 4; ++m) acc_a[m] = acc_i[m] = 0.f;
+  pdl_wait();
+  u = pdl_fresh(u);
+  for (int k0 = 0; k0 < bw; k0 += AF_GR_TK) {
+    for (int e = threadIdx.x; e < AF_GR_TM * AF_GR_TK; e += 256) {
+      const int m = e / AF_GR_TK, k = e % AF_GR_TK;
+      us[m][k] = (t0 + m < n_tokens && k0 + k < bw) ? u[(size_t)(t0 + m) * width + (size_t)b * bw + k0 + k] : 0.f;
+    }
+    for (int e = threadIdx.x; e < AF_GR_TN * AF_GR_TK; e += 256) {
+      const int n = e / AF_GR_TK, k = e % AF_GR_TK;
+      const bool in = n0 + n < bw && k0 + k < bw;
+      was[n][k] = in ? to_f32<TW>(wab[(size_t)(n0 + n) * bw + k0 + k]) : 0.f;
+      wis[n][k] = in ? to_f32<TW>(wib[(size_t)(n0 + n) * bw + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < AF_GR_TK; ++k) {
+      const float a = was[tx][k], g = wis[tx][k];
+#pragma unroll
+      for (int m = 0; m < AF_GR_TM / 4; ++m) {
+        const float v = us[ty + 4 * m][k];
+        acc_a[m] = fmaf(a, v, acc_a[m]);
+        acc_i[m] = fmaf(g, v, acc_i[m]);
+      }
+    }
+    __syncthreads();
+  }
+  if (n0 + tx >= bw) return;
+  const int c = b * bw + n0 + tx;
+  const float ab = ba[c], ib = bi[c], rt = rate[c];
+#pragma unroll
+  for (int m = 0; m < AF_GR_TM / 4; ++m) {
+    const int t = t0 + ty + 4 * m;
+    if (t >= n_tokens) continue;
+    const float r = 1.f / (1.f + expf(-(acc_a[m] + ab)));
+    const float g = 1.f / (1.f + expf(-(acc_i[m] + ib)));
+    const float la = -rt * r;                               // log a
+    const size_t at = (size_t)t * width + c;
+    decay[at] = expf(la);
+    input[at] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * g * u[at];      // sqrt(1 - a^2) i u
+  }
+}
+
+AF_EXPORT int af_gate_rows(float* decay, float* input, const float* u, const void* wa, const void* wi, int w_dtype,
+                           const float* ba, const float* bi, const float* rate, int n_tokens, int width, int blocks,
+                           cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && width > 0 && blocks > 0 && width % blocks == 0,
+             "af_gate_rows: %d channels in %d blocks", width, blocks);
+  const int bw = width / blocks;
+  const dim3 grid((n_tokens + AF_GR_TM - 1) / AF_GR_TM, blocks, (bw + AF_GR_TN - 1) / AF_GR_TN);
+  AF_REQUIRE(grid.y < 65536 && grid.z < 65536, "af_gate_rows: too many blocks of channels");
+  AF_DISPATCH_DTYPE(w_dtype, TW,
+                    af_launch(gate_rows_kernel<TW>, grid, dim3(256), 0, stream, decay, input, u, (const TW*)wa,
+                              (const TW*)wi, ba, bi, rate, n_tokens, width, bw));
+  AF_CHECK_LAUNCH("af_gate_rows");
+}
+
+// ---------------------------------------------------------------- the recurrence
+
+__device__ __forceinline__ float gelu_tanh_f32(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// A block owns 32 channels of a sequence (a lane each) and walks its tokens 128 at a time: warp w takes 16 tokens
+// in a row and composes their maps S -> a S + b, the warps exchange the pairs, each warp composes the pairs of the
+// warps before it onto the state carried so far and then walks its tokens from the state that really enters them.
+#define AF_DS_WARPS 8
+#define AF_DS_RUN 16
+template <typename TY>
+__global__ void __launch_bounds__(AF_DS_WARPS * 32)
+decay_scan_kernel(TY* __restrict__ out, const float* __restrict__ decay, const float* __restrict__ input,
+                  const float* __restrict__ proj, long long ld, int off_y, int off_x, const float* __restrict__ by,
+                  const float* __restrict__ bx, float* __restrict__ state, const int* __restrict__ seq_starts,
+                  const int* __restrict__ slots, int width, int taps) {
+  pdl_launch_dependents();
+  __shared__ float comp[AF_DS_WARPS][32][2];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  const int b = blockIdx.y;
+  const bool on = c < width;
+  const int first = seq_starts[b], last = seq_starts[b + 1];
+  const int slot = slots[b];
+  const float yb = on ? by[c] : 0.f;
+  pdl_wait();
+  decay = pdl_fresh(decay);
+  input = pdl_fresh(input);
+  proj = pdl_fresh(proj);
+  if (slot < 0) {
+    if (on)
+      for (int t = first + w; t < last; t += AF_DS_WARPS) out[(size_t)t * width + c] = from_f32<TY>(0.f);
+    return;
+  }
+  float* srow = state + (size_t)slot * taps * width;
+  float carry = on ? srow[c] : 0.f;
+  for (int base = first; base < last; base += AF_DS_WARPS * AF_DS_RUN) {
+    const int t0 = base + w * AF_DS_RUN;
+    const int n = max(0, min(AF_DS_RUN, last - t0));
+    float a[AF_DS_RUN], v[AF_DS_RUN], g[AF_DS_RUN];
+#pragma unroll
+    for (int e = 0; e < AF_DS_RUN; ++e) {
+      const bool in = on && e < n;
+      const size_t at = (size_t)(t0 + e) * width + c;
+      a[e] = in ? decay[at] : 1.f;
+      v[e] = in ? input[at] : 0.f;
+      g[e] = in ? proj[(size_t)(t0 + e) * ld + off_y + c] : 0.f;
+    }
+    float A = 1.f, B = 0.f;
+#pragma unroll
+    for (int e = 0; e < AF_DS_RUN; ++e) {
+      if (e < n) {
+        A *= a[e];
+        B = a[e] * B + v[e];
+      }
+    }
+    comp[w][lane][0] = A;
+    comp[w][lane][1] = B;
+    __syncthreads();
+    float S = carry, full = carry;
+    for (int x = 0; x < AF_DS_WARPS; ++x) {
+      if (x == w) S = full;
+      full = comp[x][lane][0] * full + comp[x][lane][1];
+    }
+    carry = full;
+#pragma unroll
+    for (int e = 0; e < AF_DS_RUN; ++e) {
+      if (e < n) {
+        S = a[e] * S + v[e];
+        if (on) out[(size_t)(t0 + e) * width + c] = from_f32<TY>(S * gelu_tanh_f32(g[e] + yb));
+      }
+    }
+    __syncthreads();
+  }
+  if (!on || w != 0) return;
+  srow[c] = carry;
+  // the convolution's last taps - 1 inputs: those of the step's last tokens, and before them what the state held
+  const int n_new = last - first;
+  const float xb = bx[c];
+  for (int j = 1; j < taps; ++j) {                      // ascending: row j only takes from rows >= j
+    const int src = n_new - (taps - j);                 // index among the step's tokens (negative: before the step)
+    float v;
+    if (src >= 0) v = proj[(size_t)(first + src) * ld + off_x + c] + xb;
+    else v = srow[(size_t)(taps + src) * width + c];
+    srow[(size_t)j * width + c] = v;
+  }
+}
+
+AF_EXPORT int af_decay_scan(void* out, int out_dtype, const float* decay, const float* input, const float* proj,
+                            long long ld, int off_y, int off_x, const float* by, const float* bx, float* state,
+                            const int* seq_starts, const int* slots, int n_seqs, int width, int taps,
+                            cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  AF_REQUIRE(n_seqs > 0 && n_seqs < 65536 && width > 0 && taps >= 1, "af_decay_scan: bad sizes");
+  AF_DISPATCH_DTYPE(out_dtype, TY,
+                    af_launch(decay_scan_kernel<TY>, dim3((width + 31) / 32, n_seqs), dim3(AF_DS_WARPS * 32), 0, stream,
+                              (TY*)out, decay, input, proj, ld, off_y, off_x, by, bx, state, seq_starts, slots, width,
+                              taps));
+  AF_CHECK_LAUNCH("af_decay_scan");
+}

@@ -938,7 +938,8 @@ def gated_scan(y, proj, off_z: int, off_x: int, off_g: int, bz, bx, state, batch
 
 def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, rot_dim: int, pairing: str,
                        q_weight=None, k_weight=None, eps: float = 0.0, v_from_k: bool = False, kv=None,
-                       bias=None, norm_after: bool = False, magnitude: float = 1.0, dv=None, pitch: int = 0) -> None:
+                       bias=None, norm_after: bool = False, magnitude: float = 1.0, dv=None, pitch: int = 0,
+                       whole_norm: bool = False) -> None:
     """From float32 projection rows [q heads | k heads (| v heads of ``dv`` values)], plus ``bias`` (float32,
     laid out like a row) when given: q and k heads normalised per head
     (x * rsqrt(mean x^2 + eps) * weight, the weight of ``hd`` values shared by the heads; no weights: as
@@ -948,7 +949,8 @@ def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, r
     compute dtype; the value heads are the raw k heads of the projection (``v_from_k``) or the projection's own.
     With ``kv`` (the layer's view of its cache pages) k and v also go to each token's row of its page.
     ``pitch`` > 0: every head of ``qkv`` and every row of the cache holds that many elements (at least ``hd`` and
-    ``dv``), zeros behind its own."""
+    ``dv``), zeros behind its own.  ``whole_norm``: q (and k) are normalised over the token's whole projection, all
+    heads at once, and the weights hold ``nq * hd`` and ``nkv * hd`` values."""
     T = proj.shape[0]
     dv = dv or hd
     pk, pv = (pitch, pitch) if pitch else (hd, dv)
@@ -959,9 +961,10 @@ def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, r
         raise KernelError(f"qk_norm_rope_store: projection of {width_in} columns into rows of {(nq + nkv) * pk + nkv * pv}")
     if pairing not in PAIRINGS or inv_freq.numel() != rot_dim // 2:
         raise KernelError("qk_norm_rope_store: pairing, or inv_freq does not hold rot_dim / 2 values")
-    for wgt in (q_weight, k_weight):
-        if wgt is not None and wgt.numel() != hd:
-            raise KernelError(f"qk_norm_rope_store: a norm weight of {hd} values")
+    for wgt, heads in ((q_weight, nq), (k_weight, nkv)):
+        want = heads * hd if whole_norm else hd
+        if (wgt is None and whole_norm) or (wgt is not None and wgt.numel() != want):
+            raise KernelError(f"qk_norm_rope_store: a norm weight of {want} values")
     if bias is not None and bias.numel() < width_in:
         raise KernelError(f"qk_norm_rope_store: a bias of {width_in} values")
     kc = vc = pt = None
@@ -984,7 +987,8 @@ def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, r
         _ptr(batch.slots, "slots", torch.int32), _ptr(batch.len_after, "len_after", torch.int32),
         _ptr(inv_freq, "inv_freq", torch.float32), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(dv), c_int(rot_dim),
         c_int(PAIRINGS[pairing]), _ptr(kc, allow_none=True), _ptr(vc, allow_none=True),
-        _ptr(pt, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring), c_int(pitch), _stream()))
+        _ptr(pt, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring), c_int(pitch),
+        c_int(1 if whole_norm else 0), _stream()))
 
 
 def attn_prefill_fast_head(size: int) -> int:
@@ -1126,6 +1130,194 @@ def add_scaled_rmsnorm(x, terms, y=None, w_next=None, eps: float = 0.0, offset: 
             c_int(dtype_code(yy.dtype) if yy is not None else F32),
             _ptr(w_next, "w_next", torch.float32, allow_none=True) if yy is not None else ctypes.c_void_p(0),
             c_int(n), c_int(H), c_float(eps), c_float(offset), _stream()))
+
+
+def _term_arg(t, n: int, H: int, who: str):
+    """Pointer, dtype code and number of partial sums of one term of a sum (a tensor [rows, H] of the
+    compute dtype or float32, or float32 partial sums [n, rows, H])."""
+    parts = 1
+    if t.dim() == 3:
+        parts = t.shape[0]
+        if t.dtype != torch.float32:
+            raise KernelError(f"{who}: partial sums are float32")
+    if tuple(t.shape[-2:]) != (n, H) or not t.is_contiguous():
+        raise KernelError(f"{who}: a term of shape {tuple(t.shape)} for rows {(n, H)}")
+    return _ptr(t), c_int(dtype_code(t.dtype)), c_int(parts)
+
+
+def add_normed_terms(x, terms, w_post, eps_post: float, offset_post: float = 0.0, y=None, w_next=None,
+                     eps_next: float = 0.0, offset_next: float = 0.0) -> None:
+    """x += norm(sum of scale * term) * (offset_post + w_post): the sum of the ``terms`` (as in
+    :func:`add_scaled_rmsnorm`) and the norm's statistics in 32 bits.  With ``y``: y = norm(x) *
+    (offset_next + w_next), or without ``w_next`` the new x itself in y's dtype.  More than two terms are
+    first added into a float32 row of their own."""
+    n, H = x.shape
+    if not x.is_contiguous() or (y is not None and not y.is_contiguous()):
+        raise KernelError("add_normed_terms: tensors must be contiguous")
+    if not terms:
+        raise KernelError("add_normed_terms: at least one term")
+    if len(terms) > 2:
+        total = torch.zeros(n, H, dtype=torch.float32, device=x.device)
+        add_scaled_rmsnorm(total, terms)
+        terms = [(total, 1.0)]
+    a, sa = terms[0]
+    b, sb = terms[1] if len(terms) > 1 else (None, 0.0)
+    barg = _term_arg(b, n, H, "add_normed_terms") if b is not None else (ctypes.c_void_p(0), c_int(F32), c_int(1))
+    _check(_lib().af_add_normed_terms(
+        _ptr(x, "x", torch.float32), *_term_arg(a, n, H, "add_normed_terms"), c_float(sa), *barg, c_float(sb),
+        _ptr(w_post, "w_post", torch.float32), c_float(eps_post), c_float(offset_post), _ptr(y, "y", allow_none=True),
+        c_int(dtype_code(y.dtype) if y is not None else F32), _ptr(w_next, "w_next", torch.float32, allow_none=True),
+        c_float(eps_next), c_float(offset_next), c_int(n), c_int(H), _stream()))
+
+
+def cast_rows(y, x, rows=None) -> None:
+    """y[r] = x[rows[r]] (or x[r]) in y's dtype; x float32 [T, H]."""
+    n, H = y.shape
+    if not (x.is_contiguous() and y.is_contiguous()) or x.shape[1] != H:
+        raise KernelError("cast_rows: contiguous tensors of one row size")
+    _check(_lib().af_cast_rows(_ptr(y, "y"), c_int(dtype_code(y.dtype)), _ptr(x, "x", torch.float32),
+                               _ptr(rows, "rows", torch.int32, allow_none=True), c_int(n), c_int(H), _stream()))
+
+
+def scale_(z, s: float) -> None:
+    """z *= s (float32, in place)."""
+    if not z.is_contiguous():
+        raise KernelError("scale_: tensor must be contiguous")
+    _check(_lib().af_scale(_ptr(z, "z", torch.float32), c_longlong(z.numel()), c_float(s), _stream()))
+
+
+# ---------------------------------------------------------------- a gated linear recurrence with a convolution in front
+
+def conv_rows(u, proj, off_x: int, bx, cw, cb, state, batch) -> None:
+    """u = the causal convolution per channel of (section ``off_x`` of the float32 projection rows + bx), plus
+    cb: ``cw`` float32 [width, taps], the last tap on the current token; the tokens before the step come from
+    rows 1 .. taps-1 of the sequence's ``state`` (float32 [slots, taps, width]; zeros for a new sequence)."""
+    T, width = u.shape
+    taps = cw.shape[1]
+    if u.dtype != torch.float32 or not u.is_contiguous() or tuple(cw.shape) != (width, taps) or not cw.is_contiguous():
+        raise KernelError(f"conv_rows: u contiguous float32 [T, {width}], taps [{width}, taps]")
+    if tuple(state.shape[1:]) != (taps, width) or state.dtype != torch.float32 or not state.is_contiguous():
+        raise KernelError(f"conv_rows: state must be contiguous float32 [slots, {taps}, {width}]")
+    if off_x + width > proj.shape[1] or bx.numel() != width or cb.numel() != width:
+        raise KernelError("conv_rows: the section lies outside the projection row, or a bias of another size")
+    pp, ld = _f32_rows(proj, "proj")
+    _check(_lib().af_conv_rows(_ptr(u), pp, ld, c_int(off_x), _ptr(bx, "bx", torch.float32), _ptr(cw, "cw", torch.float32),
+                               _ptr(cb, "cb", torch.float32), _ptr(state, "state", torch.float32),
+                               _ptr(batch.seq_of_token, "seq_of_token", torch.int32),
+                               _ptr(batch.seq_starts, "seq_starts", torch.int32), _ptr(batch.slots, "slots", torch.int32),
+                               c_int(T), c_int(width), c_int(taps), _stream()))
+
+
+def gate_rows(decay, inp, u, wa, wi, ba, bi, rate) -> None:
+    """With the channels of u (float32 [T, width]) in ``blocks`` equal parts and wa, wi [blocks, out, in]:
+    r = sigmoid(wa_b u_b + ba), i = sigmoid(wi_b u_b + bi), decay = exp(-rate r), inp = sqrt(1 - decay^2) i u
+    (all float32 [T, width]; the weights may be of the compute dtype, the sums are 32-bit)."""
+    T, width = u.shape
+    blocks, bw = wa.shape[0], wa.shape[1]
+    if blocks * bw != width or tuple(wa.shape) != (blocks, bw, bw) or wi.shape != wa.shape or wi.dtype != wa.dtype \
+            or not (wa.is_contiguous() and wi.is_contiguous()):
+        raise KernelError(f"gate_rows: gate matrices [blocks, {width} / blocks, {width} / blocks] of one dtype")
+    for t, name in ((decay, "decay"), (inp, "inp"), (u, "u")):
+        if t.dtype != torch.float32 or tuple(t.shape) != (T, width) or not t.is_contiguous():
+            raise KernelError(f"gate_rows: {name} must be contiguous float32 [{T}, {width}]")
+    if ba.numel() != width or bi.numel() != width or rate.numel() != width:
+        raise KernelError("gate_rows: biases and rates of one value a channel")
+    _check(_lib().af_gate_rows(_ptr(decay), _ptr(inp), _ptr(u), _ptr(wa), _ptr(wi), c_int(dtype_code(wa.dtype)),
+                               _ptr(ba, "ba", torch.float32), _ptr(bi, "bi", torch.float32),
+                               _ptr(rate, "rate", torch.float32), c_int(T), c_int(width), c_int(blocks), _stream()))
+
+
+def decay_scan(out, decay, inp, proj, off_y: int, off_x: int, by, bx, state, batch) -> None:
+    """S <- decay S + inp token after token from row 0 of the sequence's ``state`` (float32 [slots, taps, width];
+    left updated, with the last taps - 1 values of section ``off_x`` + bx in the rows behind it);
+    out = S * gelu_tanh(section ``off_y`` of the projection rows + by)."""
+    T, width = out.shape
+    taps = state.shape[1]
+    if not out.is_contiguous() or state.dtype != torch.float32 or tuple(state.shape[1:]) != (taps, width) \
+            or not state.is_contiguous():
+        raise KernelError(f"decay_scan: out contiguous [T, {width}], state contiguous float32 [slots, taps, {width}]")
+    for t, name in ((decay, "decay"), (inp, "inp")):
+        if t.dtype != torch.float32 or tuple(t.shape) != (T, width) or not t.is_contiguous():
+            raise KernelError(f"decay_scan: {name} must be contiguous float32 [{T}, {width}]")
+    if max(off_y, off_x) + width > proj.shape[1] or by.numel() != width or bx.numel() != width:
+        raise KernelError("decay_scan: a section lies outside the projection row, or a bias of another size")
+    pp, ld = _f32_rows(proj, "proj")
+    _check(_lib().af_decay_scan(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(decay), _ptr(inp), pp, ld, c_int(off_y),
+                                c_int(off_x), _ptr(by, "by", torch.float32), _ptr(bx, "bx", torch.float32),
+                                _ptr(state, "state", torch.float32), _ptr(batch.seq_starts, "seq_starts", torch.int32),
+                                _ptr(batch.slots, "slots", torch.int32), c_int(batch.n_seqs), c_int(width), c_int(taps),
+                                _stream()))
+
+
+# ---------------------------------------------------------------- routed experts
+
+EXPERT_TILE = 32     # pairs of one expert that a block of the experts' products takes
+
+
+def expert_max_tiles(n_pairs: int, n_experts: int) -> int:
+    """Room for the tiles of ``n_pairs`` (token, choice) pairs however they fall on the experts."""
+    return min(n_pairs, n_pairs // EXPERT_TILE + n_experts)
+
+
+def expert_route(ids, wts, shared_gate, h, router, n_experts: int) -> None:
+    """Per row of h [T, H]: scores = sigmoid(router[:n_experts] h) in 32 bits; ids, wts [T, top] = the experts
+    with the largest scores (equal scores: the lower index) and their scores; ``shared_gate`` float32 [T], when
+    given, = sigmoid(router[n_experts] h)."""
+    T, H = h.shape
+    top = ids.shape[1]
+    rows = n_experts + (1 if shared_gate is not None else 0)
+    if tuple(router.shape) != (rows, H) or router.dtype != torch.float32 or not router.is_contiguous():
+        raise KernelError(f"expert_route: router must be contiguous float32 [{rows}, {H}]")
+    if tuple(ids.shape) != (T, top) or tuple(wts.shape) != (T, top) or not (ids.is_contiguous() and wts.is_contiguous()
+                                                                           and h.is_contiguous()):
+        raise KernelError("expert_route: ids and wts contiguous [T, top], h contiguous")
+    _check(_lib().af_expert_route(_ptr(ids, "ids", torch.int32), _ptr(wts, "wts", torch.float32),
+                                  _ptr(shared_gate, "shared_gate", torch.float32, allow_none=True), _ptr(h),
+                                  c_int(dtype_code(h.dtype)), _ptr(router), c_int(T), c_int(H), c_int(n_experts),
+                                  c_int(top), _stream()))
+
+
+def expert_plan(perm, plan, ids, n_experts: int) -> None:
+    """The (token, choice) pairs of ``ids`` [T, top] sorted by expert: perm int32 [T * top] (sorted row -> pair),
+    plan int32 [1 + 3 * expert_max_tiles]: tiles in use, then (expert, first sorted row, rows) per tile."""
+    n_pairs = ids.numel()
+    max_tiles = (plan.numel() - 1) // 3
+    if perm.numel() != n_pairs or not (perm.is_contiguous() and plan.is_contiguous() and ids.is_contiguous()):
+        raise KernelError("expert_plan: one entry of perm per pair")
+    _check(_lib().af_expert_plan(_ptr(perm, "perm", torch.int32), _ptr(plan, "plan", torch.int32),
+                                 _ptr(ids, "ids", torch.int32), c_int(n_pairs), c_int(n_experts), c_int(max_tiles),
+                                 _stream()))
+
+
+def expert_rows(out, a, w0, w1=None, perm=None, plan=None, pair_weight=None, scale_out=None, n_tokens: int = 0,
+                top: int = 1, limit: float = 0.0) -> None:
+    """Rows times the matrices of the expert they belong to (the CUDA-core path; 32-bit sums in index order).
+    With ``w1``: out[sorted row] = act(s x w0[e]^T, s x w1[e]^T) * post in the compute dtype, x = row
+    pair // top of ``a``, s = pair_weight[pair], post = scale_out[token], act(g, u) = min(g, limit)
+    sigmoid(1.702 min(g, limit)) (clamp(u, +-limit) + 1).  Without: out float32 [top, tokens, N] with
+    out[choice, token] = a[sorted row] w0[e]^T.  w0, w1: [experts, N, K].  Without a plan: one expert, the
+    rows in order."""
+    n_rows = n_tokens * top
+    E, N, K = w0.shape
+    if not (a.is_contiguous() and out.is_contiguous() and w0.is_contiguous()) or a.shape[1] != K or a.dtype != w0.dtype:
+        raise KernelError("expert_rows: contiguous rows of the matrices' dtype and row size")
+    if w1 is not None:
+        if w1.shape != w0.shape or w1.dtype != w0.dtype or not w1.is_contiguous():
+            raise KernelError("expert_rows: gate and up matrices alike")
+        if tuple(out.shape) != (n_rows, N) or out.dtype != a.dtype or a.shape[0] != n_tokens:
+            raise KernelError(f"expert_rows: out [{n_rows}, {N}] of the rows' dtype")
+    elif tuple(out.shape) != (top, n_tokens, N) or out.dtype != torch.float32 or a.shape[0] != n_rows:
+        raise KernelError(f"expert_rows: out float32 [{top}, {n_tokens}, {N}] from {n_rows} rows")
+    if plan is None and E != 1:
+        raise KernelError("expert_rows: several experts need a plan")
+    max_tiles = (plan.numel() - 1) // 3 if plan is not None else 0
+    _check(_lib().af_expert_rows(_ptr(out), _ptr(a), _ptr(w0), _ptr(w1, allow_none=True), c_int(dtype_code(a.dtype)),
+                                 _ptr(perm, "perm", torch.int32, allow_none=True),
+                                 _ptr(plan, "plan", torch.int32, allow_none=True),
+                                 _ptr(pair_weight, "pair_weight", torch.float32, allow_none=True),
+                                 _ptr(scale_out, "scale_out", torch.float32, allow_none=True), c_int(n_rows),
+                                 c_int(n_tokens), c_int(top), c_int(max_tiles), c_int(N), c_int(K), c_float(limit),
+                                 _stream()))
 
 
 __all__ = [n for n in dir() if not n.startswith("_")]

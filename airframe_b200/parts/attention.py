@@ -22,7 +22,8 @@ position sees the earlier positions of its own chunk of ``window`` positions, ch
 counted from position 0) instead of the sliding one; a learned sink per head in the
 softmax's denominator; an output gate, one number per head and token (the sigmoid of
 a projection of the mixer's input), that multiplies the head's output before the
-output projection.
+output projection; and ``qk_norm`` taken over a token's whole q (and whole k)
+projection, all heads at once, with weights of that size.
 """
 from __future__ import annotations
 
@@ -47,7 +48,9 @@ class Attention(Mixer):
     result stays float32 on its way into the residual sum; optional ``value_dim`` (default ``head_dim``);
     optional ``mask`` ("window", the default, or "chunk") that says what ``window`` means; optional ``q_bias``,
     ``k_bias``, ``v_bias`` (tensor names; all or none); ``qk_norm`` may instead be {``after_rotation``: true,
-    ``eps``} (no weights: q and k over their root mean square once they are rotated); optional ``gate_weight``
+    ``eps``} (no weights: q and k over their root mean square once they are rotated), or carry ``whole``: true
+    (the mean square is taken over all heads of the token's q, and of its k, and the two weights hold
+    heads x head_dim and kv heads x head_dim values); optional ``gate_weight``
     (tensor name, [heads, hidden]: the output gate) and ``sink_weight`` (tensor name, [heads]);
     optional ``rope_epilogue`` (default false): run the
     q, k, v projection with the rotary encoding and the cache write in its epilogue
@@ -81,6 +84,9 @@ class Attention(Mixer):
         self.v_from_k = self.names[2] is None
         self.qk_norm = self.params.get("qk_norm")
         self.norm_after = bool(self.qk_norm and self.qk_norm.get("after_rotation"))
+        self.norm_whole = bool(self.qk_norm and self.qk_norm.get("whole"))
+        if self.norm_whole and self.norm_after:
+            raise ConfigError("attention: 'qk_norm' over the whole projection comes before the rotation")
         if self.qk_norm is not None:
             wanted = ("eps",) if self.norm_after else ("q_weight", "k_weight", "eps")
             missing = [k for k in wanted if k not in self.qk_norm]
@@ -133,8 +139,9 @@ class Attention(Mixer):
             decls.append(WeightDecl(v, (self.nkv * self.dv, self.hidden)))
         decls.append(WeightDecl(o, (self.hidden, self.nq * self.dv)))
         if self.qk_norm is not None and not self.norm_after:
-            decls += [WeightDecl(self.qk_norm["q_weight"], (self.hd,), "norm"),
-                      WeightDecl(self.qk_norm["k_weight"], (self.hd,), "norm")]
+            nq_w, nk_w = (self.nq * self.hd, self.nkv * self.hd) if self.norm_whole else (self.hd, self.hd)
+            decls += [WeightDecl(self.qk_norm["q_weight"], (nq_w,), "norm"),
+                      WeightDecl(self.qk_norm["k_weight"], (nk_w,), "norm")]
         for name, rows in zip(self.bias_names, (self.nq * self.hd, self.nkv * self.hd, self.nkv * self.dv)):
             if name:
                 decls.append(WeightDecl(name, (rows,), "norm"))
@@ -245,7 +252,7 @@ class Attention(Mixer):
             eps=float(self.qk_norm["eps"]) if self.qk_norm is not None else 0.0,
             v_from_k=self.v_from_k, kv=view.kv if view.writes else None, bias=self.bias,
             norm_after=self.norm_after, magnitude=rope.magnitude if rope is not None else 1.0, dv=self.dv,
-            pitch=self.pad)
+            pitch=self.pad, whole_norm=self.norm_whole)
         gate = None
         if self.gate_name:
             at = (nq + nkv) * hd + (0 if self.v_from_k else nkv * self.dv)

@@ -13,15 +13,15 @@ import torch
 
 from .. import kernels
 from ..weights.loader import WeightDecl
-from .base import Part, register_part
+from ..config.base import ConfigError, PartSpec
+from .base import Part, build_part, register_part
 from .linear import linear
 
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
-    """Parameters: ``weight``, ``vocab_size``, ``hidden_size``, ``scale``."""
-    graph_safe = True
-
+    """Parameters: ``weight``, ``vocab_size``, ``hidden_size``, ``scale``; optional ``norm`` (a PartSpec of
+    category ``norm``): applied to the gathered rows before they become the residual stream."""
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -30,12 +30,21 @@ class TokenEmbedding(Part):
         self.hidden = int(self.param("hidden_size"))
         self.scale = float(self.param("scale"))
         self.table = None
+        norm = self.params.get("norm")
+        self.norm = build_part("norm", norm, ctx) if isinstance(norm, PartSpec) else None
+
+    @property
+    def graph_safe(self):
+        return self.norm is None or self.norm.graph_safe
 
     def weight_decls(self):
-        return [WeightDecl(self.name, (self.vocab, self.hidden), "table")]
+        return [WeightDecl(self.name, (self.vocab, self.hidden), "table"),
+                *(self.norm.weight_decls() if self.norm is not None else [])]
 
     def load(self, weights):
         self.table = weights[self.name].to(self.ctx.compute_dtype).contiguous()
+        if self.norm is not None:
+            self.norm.load(weights)
 
     def decode_bytes(self, lens) -> int:
         return len(lens) * self.hidden * (4 if self.ctx.compute_dtype == torch.float32 else 2)   # the rows it gathers
@@ -44,14 +53,15 @@ class TokenEmbedding(Part):
         """ids int32 [T] -> float32 residual stream [T, H]."""
         x = torch.empty(ids.shape[0], self.hidden, dtype=torch.float32, device=ids.device)
         kernels.embed(x, self.table, ids, self.scale)
-        return x
+        return x if self.norm is None else self.norm.forward(x, torch.float32)
 
 
 @register_part("head", "lm_head")
 class LmHead(Part):
     """Parameters: ``vocab_size``, ``hidden_size``, ``softcap`` (0 = off) and
     either ``weight`` or ``tied_to`` (+ ``optional_weight`` that wins when the
-    folder holds it)."""
+    folder holds it); optional ``scale`` (default 1): the logits are multiplied by it
+    (before the softcap's place: a design has one or the other)."""
     graph_safe = True
 
 
@@ -60,6 +70,9 @@ class LmHead(Part):
         self.vocab = int(self.param("vocab_size"))
         self.hidden = int(self.param("hidden_size"))
         self.softcap = float(self.params.get("softcap") or 0.0)
+        self.scale = float(self.params.get("scale", 1.0))
+        if self.scale != 1.0 and self.softcap:
+            raise ConfigError("lm_head: a scale or a softcap, not both")
         self.w = None
         self._keys = None      # the fused arg-max's key per row (zero between calls)
 
@@ -86,7 +99,10 @@ class LmHead(Part):
 
     def forward(self, y):
         """y [R, H] compute dtype (after the final norm) -> float32 logits [R, V]."""
-        return linear(y, self.w, out_dtype=torch.float32, cap=self.softcap)
+        logits = linear(y, self.w, out_dtype=torch.float32, cap=self.softcap)
+        if self.scale != 1.0:
+            kernels.scale_(logits, self.scale)
+        return logits
 
     def forward_argmax(self, y):
         """The token of greedy decoding for every row: int32 [R], the arg-max of
@@ -95,7 +111,7 @@ class LmHead(Part):
         epilogue keeps the best per row); else logits and the sampler's arg-max."""
         R = y.shape[0]
         tokens = torch.empty(R, dtype=torch.int32, device=y.device)
-        if kernels.gemm_tc_supported(y, self.w, None):
+        if kernels.gemm_tc_supported(y, self.w, None) and self.scale > 0:      # (a positive scale moves no arg-max)
             stride = kernels.argmax_key_stride()
             if self._keys is None or self._keys.numel() < R * stride:
                 self._keys = torch.zeros(max(R, 256) * stride, dtype=torch.int64, device=y.device)

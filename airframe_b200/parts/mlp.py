@@ -3,6 +3,16 @@
 Reference: ``src/backend/bindless/sh_layer_v1.wgsl:1024-1070`` (gate and up),
 ``:1079`` (tanh-GELU), ``:1082`` (SiLU), ``:1104-1140`` (down).  The reference
 picks the activation by a proxy (softcap > 0); here it is a parameter.
+
+``routed_experts``: a mixture of small feed-forwards of which a token uses a
+few.  The router's scores are sigmoids of its logits (32-bit), the ``top``
+largest choose the experts, and a chosen expert's score multiplies the expert's
+*input*: f = sum over the chosen e of E_e(s_e h), with E(h) = W_down (act(W_gate h,
+W_up h)) and act(g, u) = g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit),
+u' = clamp(u, -limit, limit).  A shared expert of the same form (own size and limit)
+may run for every token; it is added times sigmoid(w_sg . h).  Nothing is read back
+by the host: the pairs are sorted by expert on the device and the products walk
+tiles of one expert's pairs, so a decode step can be captured.
 """
 from __future__ import annotations
 
@@ -12,7 +22,7 @@ from .. import kernels
 from ..config.base import ConfigError
 from ..weights.loader import WeightDecl
 from .base import FeedForward, register_part
-from .linear import gated_linear, linear_split
+from .linear import PartialSums, WeightedSum, gated_linear, linear_split
 
 
 @register_part("feed_forward", "gated_mlp")
@@ -73,3 +83,102 @@ class NoFeedForward(FeedForward):
 
     def forward(self, x, batch):
         raise ConfigError("a layer without a feed-forward was asked to run one (its block does not leave it out)")
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    """Parameters: ``hidden_size``, ``intermediate_size``, ``num_experts``, ``top``, ``limit``,
+    ``router_weight`` ([experts, hidden]) and ``expert_weights``: a pattern with ``{e}`` for the expert's number
+    and ``{role}`` for gate / up / down; optional ``shared``: {``intermediate_size``, ``limit``,
+    ``gate_weight``, ``up_weight``, ``down_weight``, ``mix_weight`` ([1, hidden])}.  The result is a sum of
+    32-bit terms that the residual kernel takes."""
+    graph_safe = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(self.param("hidden_size"))
+        self.inter = int(self.param("intermediate_size"))
+        self.n_experts = int(self.param("num_experts"))
+        self.top = int(self.param("top"))
+        self.limit = float(self.param("limit"))
+        if not 1 <= self.top <= self.n_experts:
+            raise ConfigError(f"routed_experts: {self.top} of {self.n_experts} experts")
+        self.router_name = self.param("router_weight")
+        self.pattern = self.param("expert_weights")
+        self.shared = self.params.get("shared")
+        if self.shared is not None:
+            missing = [k for k in ("intermediate_size", "limit", "gate_weight", "up_weight", "down_weight", "mix_weight")
+                       if k not in self.shared]
+            if missing:
+                raise ConfigError(f"routed_experts: 'shared' needs {missing}")
+
+    def _name(self, e: int, role: str) -> str:
+        return self.pattern.format(e=e, role=role)
+
+    def weight_decls(self):
+        h, f = self.hidden, self.inter
+        decls = [WeightDecl(self.router_name, (self.n_experts, h))]
+        for e in range(self.n_experts):
+            decls += [WeightDecl(self._name(e, "gate"), (f, h)), WeightDecl(self._name(e, "up"), (f, h)),
+                      WeightDecl(self._name(e, "down"), (h, f))]
+        if self.shared is not None:
+            sf, sh = int(self.shared["intermediate_size"]), self.shared
+            decls += [WeightDecl(sh["gate_weight"], (sf, h)), WeightDecl(sh["up_weight"], (sf, h)),
+                      WeightDecl(sh["down_weight"], (h, sf)), WeightDecl(sh["mix_weight"], (1, h))]
+        return decls
+
+    def load(self, weights):
+        dt = self.ctx.compute_dtype
+        E = range(self.n_experts)
+        self.w_gate = torch.stack([weights[self._name(e, "gate")] for e in E]).to(dt).contiguous()
+        self.w_up = torch.stack([weights[self._name(e, "up")] for e in E]).to(dt).contiguous()
+        self.w_down = torch.stack([weights[self._name(e, "down")] for e in E]).to(dt).contiguous()
+        rows = [weights[self.router_name]]
+        if self.shared is not None:
+            sh = self.shared
+            rows.append(weights[sh["mix_weight"]].reshape(1, self.hidden))       # the shared expert's gate rides with the router
+            self.s_gate = weights[sh["gate_weight"]].to(dt).unsqueeze(0).contiguous()
+            self.s_up = weights[sh["up_weight"]].to(dt).unsqueeze(0).contiguous()
+            self.s_down = weights[sh["down_weight"]].to(dt).unsqueeze(0).contiguous()
+        self.router = torch.cat(rows, dim=0).to(torch.float32).contiguous()      # (router logits are 32-bit)
+
+    def _el(self) -> int:
+        return 4 if self.ctx.compute_dtype == torch.float32 else 2
+
+    def decode_bytes(self, lens) -> int:
+        used = min(self.n_experts, len(lens) * self.top)        # at most so many experts' matrices are read
+        total = 3 * used * self.hidden * self.inter * self._el() + 4 * self.router.numel()
+        if self.shared is not None:
+            total += 3 * self.hidden * int(self.shared["intermediate_size"]) * self._el()
+        return total
+
+    def prefill_flops(self, lens) -> int:
+        per_token = 3 * self.hidden * self.inter * self.top + self.router.numel()
+        if self.shared is not None:
+            per_token += 3 * self.hidden * int(self.shared["intermediate_size"])
+        return 2 * sum(lens) * per_token
+
+    def forward(self, x, batch):
+        T, top, dev = x.shape[0], self.top, x.device
+        ids = torch.empty(T, top, dtype=torch.int32, device=dev)
+        wts = torch.empty(T, top, dtype=torch.float32, device=dev)
+        mix = torch.empty(T, dtype=torch.float32, device=dev) if self.shared is not None else None
+        kernels.expert_route(ids, wts, mix, x, self.router, self.n_experts)
+        perm = torch.empty(T * top, dtype=torch.int32, device=dev)
+        plan = torch.empty(1 + 3 * kernels.expert_max_tiles(T * top, self.n_experts), dtype=torch.int32, device=dev)
+        kernels.expert_plan(perm, plan, ids, self.n_experts)
+        mid = torch.empty(T * top, self.inter, dtype=x.dtype, device=dev)
+        kernels.expert_rows(mid, x, self.w_gate, self.w_up, perm=perm, plan=plan, pair_weight=wts, n_tokens=T, top=top,
+                            limit=self.limit)
+        out = torch.empty(top, T, self.hidden, dtype=torch.float32, device=dev)
+        kernels.expert_rows(out, mid, self.w_down, perm=perm, plan=plan, n_tokens=T, top=top)
+        terms = [(PartialSums(out), 1.0)]
+        if self.shared is not None:
+            sf = int(self.shared["intermediate_size"])
+            smid = torch.empty(T, sf, dtype=x.dtype, device=dev)
+            kernels.expert_rows(smid, x, self.s_gate, self.s_up, scale_out=mix, n_tokens=T, top=1,
+                                limit=float(self.shared["limit"]))
+            sout = torch.empty(1, T, self.hidden, dtype=torch.float32, device=dev)
+            kernels.expert_rows(sout, smid, self.s_down, n_tokens=T, top=1)
+            terms.append((sout[0], 1.0))
+        return WeightedSum(terms)

@@ -3,6 +3,8 @@
 ``rms_norm``: y = x * rsqrt(mean(x^2) + eps) * (offset + w).
 ``tanh_norm``: y = tanh(alpha x) w + b with a scalar alpha: no mean and no
 variance, so it is elementwise and a row needs no reduction.
+``as_is``: y = x in the compute dtype: what a sublayer is given that reads the
+stream itself (a norm only behind it); a residual kernel writes it beside the sum.
 
 Reference: ``src/backend/bindless/sh_layer_v1.wgsl:426-451``,
 ``src/backend/bindless/sh_rmsnorm.wgsl:69-93``; post norms fused with the
@@ -50,6 +52,26 @@ class RmsNorm(Norm):
         return y
 
     def add_normed(self, x, a, then=None, out_dtype=None):
+        """x += this norm of ``a`` (a tensor, partial sums, or a weighted sum of those, which is taken in 32
+        bits under the norm); with ``then`` its output for the new x, out of the same kernel where that
+        kernel exists (another ``rms_norm``, or ``as_is``)."""
+        terms = as_terms(a)
+        plain = len(terms) == 1 and terms[0][1] == 1.0
+        same = isinstance(then, RmsNorm) and then.offset == self.offset
+        if not plain or isinstance(then, AsIs) or (isinstance(then, RmsNorm) and not same):
+            fused = then is None or isinstance(then, (RmsNorm, AsIs))
+            y = None
+            alias = isinstance(then, AsIs) and out_dtype == torch.float32      # (the 32-bit stream is its own copy)
+            if then is not None and fused and not alias:
+                y = torch.empty(x.shape[0], self.size, dtype=out_dtype, device=x.device)
+            nxt = then if isinstance(then, RmsNorm) else None
+            kernels.add_normed_terms(x, terms, self.w, self.eps, self.offset, y=y,
+                                     w_next=nxt.w if nxt is not None else None,
+                                     eps_next=nxt.eps if nxt is not None else 0.0,
+                                     offset_next=nxt.offset if nxt is not None else 0.0)
+            if alias:
+                return x
+            return y if fused else then.forward(x, out_dtype)
         n_parts = 1
         if isinstance(a, PartialSums):
             n_parts, a = a.parts.shape[0], a.parts
@@ -118,3 +140,33 @@ class TanhNorm(Norm):
                               b_next=then.b if then is not None else None,
                               alpha_next=then.alpha if then is not None else 0.0)
         return y
+
+
+@register_part("norm", "as_is")
+class AsIs(Norm):
+    """No norm at all: the residual stream as it stands, in the dtype asked for.  Parameters: ``size``.  It
+    stands where a block wants "the norm in front of a sublayer" and the design has none there; the residual
+    kernels of the other norms write its output beside their sum (``add_normed(..., then=)``)."""
+    graph_safe = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.size = int(self.param("size"))
+
+    def forward(self, x, out_dtype, rows=None):
+        if rows is None and out_dtype == torch.float32:
+            return x                    # (the sublayer reads the stream itself; it is rewritten only once the sublayer is done)
+        n = x.shape[0] if rows is None else rows.shape[0]
+        y = torch.empty(n, self.size, dtype=out_dtype, device=x.device)
+        kernels.cast_rows(y, x, rows)
+        return y
+
+    def add_normed(self, x, a, then=None, out_dtype=None):
+        if then is not None:
+            return then.after_add(x, a, out_dtype)
+        kernels.add_scaled_rmsnorm(x, as_terms(a))
+        return None
+
+    def after_add(self, x, a, out_dtype):
+        kernels.add_scaled_rmsnorm(x, as_terms(a))
+        return self.forward(x, out_dtype)

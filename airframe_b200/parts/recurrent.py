@@ -21,6 +21,13 @@ together are RMS-normed with a weight vector (no offset), times sigmoid(Wg h), t
 c = Wx h + bx, candidate = c + 1/2 where c >= 0 and sigmoid(c) below,
 S <- (1 - z) S + z * candidate, output Wo (S * silu(Wg h)).
 
+``rglru``: a real-gated linear recurrence behind a short causal convolution (the
+recurrent block of Griffin): y = gelu_tanh(Wy h + by), u = conv(Wx h + bx) per
+channel; with the channels in ``blocks`` equal parts and block-diagonal gate
+matrices, r = sigmoid(Wa u + ba), i = sigmoid(Wi u + bi), a = exp(-decay_rate r
+softplus(lam)), S <- a S + sqrt(1 - a^2) i u, output Wo (S * y).  The state of a
+sequence is S and the convolution's last taps - 1 inputs.
+
 Every projection of a mixer is one product into 32-bit rows; what enters a
 recurrence (decays, gates, unit keys) is worked out in 32 bits from them.
 """
@@ -236,4 +243,74 @@ class MinGru(_StateMixer):
         proj = linear(x, self.w_in, out_dtype=torch.float32)
         y = torch.empty(x.shape[0], self.width, dtype=x.dtype, device=x.device)
         kernels.gated_scan(y, proj, off["z"], off["x"], off["g"], self.z_bias, self.x_bias, view.state, batch)
+        return linear_split(y, self.w_o, wide=self.wide)
+
+
+@register_part("mixer", "rglru")
+class RgLru(_StateMixer):
+    """Parameters: ``hidden_size``, ``width`` (of the state), ``blocks`` (of the gates' block-diagonal
+    matrices), ``taps`` (of the convolution), ``weights``: tensor names for ``y, y_bias, x, x_bias, conv
+    ([width, taps], the last column on the current token), conv_bias, a ([blocks, width / blocks, width /
+    blocks], [out, in]), a_bias ([blocks, width / blocks]), i, i_bias, lam, o``; optional ``decay_rate``
+    (default 8)."""
+    ROLES = ("y", "y_bias", "x", "x_bias", "conv", "conv_bias", "a", "a_bias", "i", "i_bias", "lam", "o")
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(self.param("hidden_size"))
+        self.width = int(self.param("width"))
+        self.blocks = int(self.param("blocks"))
+        self.taps = int(self.param("taps"))
+        self.decay_rate = float(self.params.get("decay_rate", 8.0))
+        if self.blocks < 1 or self.width % self.blocks:
+            raise ConfigError(f"rglru: {self.width} channels do not come in {self.blocks} equal blocks")
+        if self.taps < 1:
+            raise ConfigError("rglru: the convolution has at least the current token's tap")
+        self.names = self._names(self.ROLES)
+
+    def state_need(self):
+        return StateNeed((self.taps, self.width), "float32")      # row 0: S; then the convolution's last inputs
+
+    def weight_decls(self):
+        w, h, b, nm = self.width, self.hidden, self.blocks, self.names
+        bw = w // b
+        return [WeightDecl(nm["y"], (w, h)), WeightDecl(nm["y_bias"], (w,), "norm"),
+                WeightDecl(nm["x"], (w, h)), WeightDecl(nm["x_bias"], (w,), "norm"),
+                WeightDecl(nm["conv"], (w, self.taps), "gain"), WeightDecl(nm["conv_bias"], (w,), "norm"),
+                WeightDecl(nm["a"], (b, bw, bw)), WeightDecl(nm["a_bias"], (b, bw), "norm"),
+                WeightDecl(nm["i"], (b, bw, bw)), WeightDecl(nm["i_bias"], (b, bw), "norm"),
+                WeightDecl(nm["lam"], (w,), "gain"), WeightDecl(nm["o"], (h, w))]
+
+    def load(self, weights):
+        nm, f32, dt = self.names, torch.float32, self.ctx.compute_dtype
+        self.w_in, self.off = self._pack(weights, ("y", "x"))
+        self.y_bias = weights[nm["y_bias"]].to(f32).contiguous()
+        self.x_bias = weights[nm["x_bias"]].to(f32).contiguous()
+        self.conv_w = weights[nm["conv"]].to(f32).contiguous()
+        self.conv_b = weights[nm["conv_bias"]].to(f32).contiguous()
+        self.w_a = weights[nm["a"]].to(dt).contiguous()
+        self.w_i = weights[nm["i"]].to(dt).contiguous()
+        self.a_bias = weights[nm["a_bias"]].to(f32).reshape(-1).contiguous()
+        self.i_bias = weights[nm["i_bias"]].to(f32).reshape(-1).contiguous()
+        # decay_rate * softplus(lam), once, from the stored values (worked out in 64 bits, kept in 32)
+        self.rate = (self.decay_rate * torch.nn.functional.softplus(weights[nm["lam"]].to(torch.float64))).to(f32).contiguous()
+        self.w_o = weights[nm["o"]].to(dt).contiguous()
+
+    def decode_bytes(self, lens) -> int:
+        weights = (self.w_in.numel() + self.w_o.numel() + self.w_a.numel() + self.w_i.numel()) * _el(self.ctx)
+        return weights + len(lens) * 2 * 4 * self.taps * self.width
+
+    def prefill_flops(self, lens) -> int:
+        return 2 * sum(lens) * (self.w_in.numel() + self.w_o.numel() + self.w_a.numel() + self.w_i.numel())
+
+    def forward(self, x, batch, view):
+        T, w, off, f32 = x.shape[0], self.width, self.off, torch.float32
+        proj = linear(x, self.w_in, out_dtype=f32)
+        u = torch.empty(T, w, dtype=f32, device=x.device)
+        kernels.conv_rows(u, proj, off["x"], self.x_bias, self.conv_w, self.conv_b, view.state, batch)
+        decay = torch.empty(T, w, dtype=f32, device=x.device)
+        inp = torch.empty(T, w, dtype=f32, device=x.device)
+        kernels.gate_rows(decay, inp, u, self.w_a, self.w_i, self.a_bias, self.i_bias, self.rate)
+        y = torch.empty(T, w, dtype=x.dtype, device=x.device)
+        kernels.decay_scan(y, decay, inp, proj, off["y"], off["x"], self.y_bias, self.x_bias, view.state, batch)
         return linear_split(y, self.w_o, wide=self.wide)

@@ -14,6 +14,10 @@ turn(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(tu
 hi = min(ceil(turn(slow)), rotary_dim - 1), pair p gets the ramp r = clamp((p - lo) / max(hi - lo, 0.001), 0, 1) and
 the frequency f_p / factor * r + f_p * (1 - r): fast pairs keep their frequency, slow ones are
 divided by ``factor``.  Cosines and sines are then multiplied by ``magnitude`` = 0.1 ln(factor) + 1.
+
+``scaling`` with ``kind`` = "wavelength" ({factor, low, high, original}) decides pair by pair from the
+wavelength l = 2 pi / f: l < original / high keeps f; l > original / low takes f / factor; between the two,
+with s = (original / l - low) / (high - low), the frequency is (1 - s) f / factor + s f.  No magnitude.
 """
 from __future__ import annotations
 
@@ -29,7 +33,7 @@ from .base import PositionEncoding, register_part
 @register_part("position", "rope")
 class Rope(PositionEncoding):
     """Parameters: ``theta``, ``rotary_dim``, ``pairing``; optional ``scaling``: {``factor``, ``original``,
-    ``fast``, ``slow``}."""
+    ``fast``, ``slow``}, or {``kind``: "wavelength", ``factor``, ``low``, ``high``, ``original``}."""
     graph_safe = True
 
 
@@ -46,7 +50,20 @@ class Rope(PositionEncoding):
         inv = torch.tensor(self.theta, dtype=torch.float64) ** (-2.0 * p / max(self.rotary_dim, 1))
         self.magnitude = 1.0
         sc = self.params.get("scaling")
-        if sc:
+        if sc and sc.get("kind", "ramp") not in ("ramp", "wavelength"):
+            raise ConfigError(f"rope: unknown kind of 'scaling' '{sc.get('kind')}' (known: ramp, wavelength)")
+        if sc and sc.get("kind") == "wavelength":
+            missing = [k for k in ("factor", "low", "high", "original") if k not in sc]
+            if missing:
+                raise ConfigError(f"rope: 'scaling' needs {missing}")
+            factor, low, high, original = (float(sc[k]) for k in ("factor", "low", "high", "original"))
+            if not (factor > 0 and original > 0 and low > 0 and high > low):
+                raise ConfigError("rope: 'scaling' by wavelength needs positive numbers and high > low")
+            wave = 2.0 * math.pi / inv
+            s = (original / wave - low) / (high - low)
+            mixed = (1.0 - s) * inv / factor + s * inv
+            inv = torch.where(wave < original / high, inv, torch.where(wave > original / low, inv / factor, mixed))
+        elif sc:
             missing = [k for k in ("factor", "original", "fast", "slow") if k not in sc]
             if missing:
                 raise ConfigError(f"rope: 'scaling' needs {missing}")
