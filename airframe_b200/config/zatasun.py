@@ -137,7 +137,8 @@ class ZatasunConfig(ModelConfig):
         h, eps = self.width, self.norm_eps
         left, right = m["left"], m["right"]
         lp, rp = p + "left.", p + "right."
-        rot = {"theta": float(left["rot"]["base"]), "rotary_dim": left["rot"]["dims"], "pairing": "half"}
+        rot = {"theta": float(left["rot"]["base"]), "rotary_dim": left["rot"]["dims"], "pairing": "half",
+               "precise_angles": True}
         if left["rot"].get("scaling") is not None:
             sc = left["rot"]["scaling"]
             rot["scaling"] = {"kind": "wavelength", "factor": float(sc["factor"]), "low": float(sc["low"]),

@@ -246,6 +246,30 @@ __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restr
   }
 }
 
+// The same from 64-bit frequencies, the angle and its reduction in 64 bits (a position of some thousands times a
+// frequency near 1 loses the last bits of a 32-bit angle): for designs whose tolerance is that of 32-bit logits.
+__global__ void rope_table_precise_kernel(float2* __restrict__ table, const int* __restrict__ positions,
+                                          const double* __restrict__ inv_freq, int half) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const double pos = (double)positions[t];
+  for (int p = threadIdx.x; p < half; p += blockDim.x) {
+    double s, c;
+    sincos(pos * inv_freq[p], &s, &c);
+    table[(size_t)t * half + p] = make_float2((float)c, (float)s);
+  }
+}
+
+AF_EXPORT int af_rope_table_precise(float* table, const int* positions, const double* inv_freq, int n_tokens, int half,
+                                    cudaStream_t stream) {
+  if (n_tokens == 0 || half == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && half > 0 && ((uintptr_t)table & 7) == 0, "af_rope_table_precise: bad sizes");
+  af_launch(rope_table_precise_kernel, dim3(n_tokens), dim3(half < 32 ? 32 : (half > 256 ? 256 : half)), 0, stream,
+            reinterpret_cast<float2*>(table), positions, inv_freq, half);
+  AF_CHECK_LAUNCH("af_rope_table_precise");
+}
+
 AF_EXPORT int af_rope_table(float* table, const int* positions, const float* inv_freq, int n_tokens, int half,
                             cudaStream_t stream) {
   if (n_tokens == 0 || half == 0) return 0;
@@ -655,7 +679,8 @@ template <typename T>
 __device__ __forceinline__ void qk_pack_head(T* __restrict__ qkv, long long out_stride, const float* __restrict__ proj,
                                              long long ld, const float* __restrict__ bias, const float* __restrict__ w,
                                              bool whole, float inv_whole, float eps, int norm_after, float magnitude,
-                                             int v_from_k, const float* __restrict__ inv_freq, int nq, int nkv, int hd,
+                                             int v_from_k, const float* __restrict__ inv_freq,
+                                             const float2* __restrict__ table, int nq, int nkv, int hd,
                                              int dv, int rot_dim, int pairing, int pk, int pv, int t, int head, int pos,
                                              int lane, T* kdst, T* vdst) {
   const bool is_k = head >= nq;
@@ -694,7 +719,12 @@ __device__ __forceinline__ void qk_pack_head(T* __restrict__ qkv, long long out_
     float a = x[i0] + (xb ? xb[i0] : 0.f), b = x[i1] + (xb ? xb[i1] : 0.f);
     if (w) a *= inv * w[i0], b *= inv * w[i1];
     float s, c;
-    sincosf((float)pos * inv_freq[p], &s, &c);
+    if (table != nullptr) {                     // the step's table of (cos, sin) per token and pair
+      const float2 cs = table[(size_t)t * half + p];
+      c = cs.x, s = cs.y;
+    } else {
+      sincosf((float)pos * inv_freq[p], &s, &c);
+    }
     s *= magnitude, c *= magnitude;
     const T ra = from_f32<T>((a * c - b * s) * after), rb = from_f32<T>((b * c + a * s) * after);
     dst[i0] = ra, dst[i1] = rb;
@@ -732,7 +762,8 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float
                           const float* __restrict__ k_weight, float eps, int norm_after, float magnitude,
                           int v_from_k, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                           const int* __restrict__ slots, const int* __restrict__ len_after,
-                          const float* __restrict__ inv_freq, int n_tokens, int nq, int nkv, int hd, int dv, int rot_dim,
+                          const float* __restrict__ inv_freq, const float2* __restrict__ table, int n_tokens, int nq,
+                          int nkv, int hd, int dv, int rot_dim,
                           int pairing, T* __restrict__ kcache, T* __restrict__ vcache,
                           const int* __restrict__ page_table, int max_pages, int ring_rows, int pitch) {
   pdl_launch_dependents();
@@ -748,7 +779,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const float
                   head - nq, pk, pv, &kdst, &vdst);
   pdl_wait();
   qk_pack_head(qkv, out_stride, proj, ld, bias, head >= nq ? k_weight : q_weight, false, 1.f, eps, norm_after, magnitude,
-               v_from_k, inv_freq, nq, nkv, hd, dv, rot_dim, pairing, pk, pv, t, head, pos, lane, kdst, vdst);
+               v_from_k, inv_freq, table, nq, nkv, hd, dv, rot_dim, pairing, pk, pv, t, head, pos, lane, kdst, vdst);
 }
 
 // The same with q (and k) normed over the whole projection of the token, all heads at once: the weights hold
@@ -760,7 +791,8 @@ qk_whole_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const
                                 const float* __restrict__ k_weight, float eps, int norm_after, float magnitude,
                                 int v_from_k, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                 const int* __restrict__ slots, const int* __restrict__ len_after,
-                                const float* __restrict__ inv_freq, int nq, int nkv, int hd, int dv, int rot_dim,
+                                const float* __restrict__ inv_freq, const float2* __restrict__ table, int nq, int nkv,
+                                int hd, int dv, int rot_dim,
                                 int pairing, T* __restrict__ kcache, T* __restrict__ vcache,
                                 const int* __restrict__ page_table, int max_pages, int ring_rows, int pitch) {
   pdl_launch_dependents();
@@ -788,7 +820,7 @@ qk_whole_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const
                     head - nq, pk, pv, &kdst, &vdst);
     const float* w = is_k ? k_weight + (size_t)(head - nq) * hd : q_weight + (size_t)head * hd;
     qk_pack_head(qkv, out_stride, proj, ld, bias, w, true, is_k ? inv_k : inv_q, eps, norm_after, magnitude, v_from_k,
-                 inv_freq, nq, nkv, hd, dv, rot_dim, pairing, pk, pv, t, head, pos, lane, kdst, vdst);
+                 inv_freq, table, nq, nkv, hd, dv, rot_dim, pairing, pk, pv, t, head, pos, lane, kdst, vdst);
   }
 }
 
@@ -796,9 +828,12 @@ AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, 
                                     const float* bias, const float* q_weight, const float* k_weight, float eps,
                                     int norm_after, float magnitude, int v_from_k,
                                     const int* positions, const int* seq_of_token, const int* slots,
-                                    const int* len_after, const float* inv_freq, int n_tokens, int nq, int nkv, int hd,
+                                    const int* len_after, const float* inv_freq, const float* table, int n_tokens,
+                                    int nq, int nkv, int hd,
                                     int dv, int rot_dim, int pairing, void* kcache, void* vcache, const int* page_table,
                                     int max_pages, int ring_rows, int pitch, int whole_norm, cudaStream_t stream) {
+  const float2* tab = reinterpret_cast<const float2*>(table);
+  AF_REQUIRE(((uintptr_t)table & 7) == 0, "af_qk_norm_rope_store: the table of cosines and sines lies on 8 bytes");
   if (n_tokens == 0) return 0;
   AF_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && hd > 0 && dv > 0, "af_qk_norm_rope_store: bad sizes");
   AF_REQUIRE(!whole_norm || q_weight != nullptr, "af_qk_norm_rope_store: a norm over the whole projection needs its weights");
@@ -815,7 +850,7 @@ AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, 
     AF_DISPATCH_DTYPE(dtype, T,
                       af_launch(qk_whole_norm_rope_store_kernel<T>, dim3((unsigned)n_tokens), dim3(256), 0, stream, (T*)qkv,
                                 out_stride, proj, ld, bias, q_weight, k_weight, eps, norm_after, magnitude, v_from_k,
-                                positions, seq_of_token, slots, len_after, inv_freq, nq, nkv, hd, dv, rot_dim, pairing,
+                                positions, seq_of_token, slots, len_after, inv_freq, tab, nq, nkv, hd, dv, rot_dim, pairing,
                                 (T*)kcache, (T*)vcache, page_table, max_pages, ring_rows, pitch));
     AF_CHECK_LAUNCH("af_qk_norm_rope_store");
   }
@@ -825,7 +860,7 @@ AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, 
   AF_DISPATCH_DTYPE(dtype, T,
                     af_launch(qk_norm_rope_store_kernel<T>, dim3((unsigned)blocks), dim3(128), 0, stream, (T*)qkv,
                               out_stride, proj, ld, bias, q_weight, k_weight, eps, norm_after, magnitude, v_from_k,
-                              positions, seq_of_token, slots, len_after, inv_freq, n_tokens, nq, nkv, hd, dv, rot_dim,
+                              positions, seq_of_token, slots, len_after, inv_freq, tab, n_tokens, nq, nkv, hd, dv, rot_dim,
                               pairing, (T*)kcache, (T*)vcache, page_table, max_pages, ring_rows, pitch));
   AF_CHECK_LAUNCH("af_qk_norm_rope_store");
 }

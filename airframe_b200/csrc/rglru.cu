@@ -5,7 +5,9 @@
 //               taken from the sequence's state;
 //   gate_rows   r = sigmoid(Wa_b u_b + ba), i = sigmoid(Wi_b u_b + bi) with block-diagonal Wa, Wi (b = the
 //               block of channels), then a = exp(-c r softplus(lam)) and the token's input sqrt(1 - a^2) i u;
-//   decay_scan  S <- a S + input token after token, out = S * gelu_tanh(y + by), and the state left for the next
+//               what is kept of a is 1 - a = -expm1(log a): a itself, rounded to 32 bits next to 1, would lose
+//               most of the bits that say how fast a slow channel forgets;
+//   decay_scan  S <- a S + input = S - (1 - a) S + input token after token, out = S * gelu_tanh(y + by), and the state left for the next
 //               step: S and the last taps - 1 inputs of the convolution.
 // Everything here is 32-bit: the rows come from products that accumulate in 32 bits, the weights of the gates are
 // read in the compute dtype and widened, and only the output (the input of the output product) is of the compute dtype.
@@ -118,7 +120,7 @@ gate_rows_kernel(float* __restrict__ decay, float* __restrict__ input, const flo
     const float g = 1.f / (1.f + expf(-(acc_i[m] + ib)));
     const float la = -rt * r;                               // log a
     const size_t at = (size_t)t * width + c;
-    decay[at] = expf(la);
+    decay[at] = -expm1f(la);                                // 1 - a
     input[at] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * g * u[at];      // sqrt(1 - a^2) i u
   }
 }
@@ -145,7 +147,8 @@ __device__ __forceinline__ float gelu_tanh_f32(float z) {
 }
 
 // A block owns 32 channels of a sequence (a lane each) and walks its tokens 128 at a time: warp w takes 16 tokens
-// in a row and composes their maps S -> a S + b, the warps exchange the pairs, each warp composes the pairs of the
+// in a row and composes their maps S -> S - d S + b (d = 1 - a; two such maps compose to d = d1 + d2 - d1 d2),
+// the warps exchange the pairs, each warp composes the pairs of the
 // warps before it onto the state carried so far and then walks its tokens from the state that really enters them.
 #define AF_DS_WARPS 8
 #define AF_DS_RUN 16
@@ -183,16 +186,16 @@ decay_scan_kernel(TY* __restrict__ out, const float* __restrict__ decay, const f
     for (int e = 0; e < AF_DS_RUN; ++e) {
       const bool in = on && e < n;
       const size_t at = (size_t)(t0 + e) * width + c;
-      a[e] = in ? decay[at] : 1.f;
+      a[e] = in ? decay[at] : 0.f;                 // 1 - a of the token
       v[e] = in ? input[at] : 0.f;
       g[e] = in ? proj[(size_t)(t0 + e) * ld + off_y + c] : 0.f;
     }
-    float A = 1.f, B = 0.f;
+    float A = 0.f, B = 0.f;                        // the stretch's map: S -> S - A S + B
 #pragma unroll
     for (int e = 0; e < AF_DS_RUN; ++e) {
       if (e < n) {
-        A *= a[e];
-        B = a[e] * B + v[e];
+        A = fmaf(-A, a[e], A + a[e]);
+        B = fmaf(-a[e], B, B) + v[e];
       }
     }
     comp[w][lane][0] = A;
@@ -201,13 +204,13 @@ decay_scan_kernel(TY* __restrict__ out, const float* __restrict__ decay, const f
     float S = carry, full = carry;
     for (int x = 0; x < AF_DS_WARPS; ++x) {
       if (x == w) S = full;
-      full = comp[x][lane][0] * full + comp[x][lane][1];
+      full = fmaf(-comp[x][lane][0], full, full) + comp[x][lane][1];
     }
     carry = full;
 #pragma unroll
     for (int e = 0; e < AF_DS_RUN; ++e) {
       if (e < n) {
-        S = a[e] * S + v[e];
+        S = fmaf(-a[e], S, S) + v[e];
         if (on) out[(size_t)(t0 + e) * width + c] = from_f32<TY>(S * gelu_tanh_f32(g[e] + yb));
       }
     }

@@ -490,6 +490,15 @@ def rope_table(positions, inv_freq) -> torch.Tensor:
     return table
 
 
+def rope_table_precise(positions, inv_freq64) -> torch.Tensor:
+    """The same table from float64 frequencies with the angle and its reduction in 64 bits."""
+    T, half = positions.shape[0], inv_freq64.numel()
+    table = torch.empty(T, half, 2, dtype=torch.float32, device=positions.device)
+    _check(_lib().af_rope_table_precise(_ptr(table), _ptr(positions, "positions", torch.int32),
+                                        _ptr(inv_freq64, "inv_freq", torch.float64), c_int(T), c_int(half), _stream()))
+    return table
+
+
 def kv_rows(batch, kv, nkv: int) -> torch.Tensor:
     """int32 [T]: each token's row in the cache pages of ``kv`` (a layer's view;
     all layers of its group share the page table) for kv head 0, -1 for tokens
@@ -939,7 +948,7 @@ def gated_scan(y, proj, off_z: int, off_x: int, off_g: int, bz, bx, state, batch
 def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, rot_dim: int, pairing: str,
                        q_weight=None, k_weight=None, eps: float = 0.0, v_from_k: bool = False, kv=None,
                        bias=None, norm_after: bool = False, magnitude: float = 1.0, dv=None, pitch: int = 0,
-                       whole_norm: bool = False) -> None:
+                       whole_norm: bool = False, table=None) -> None:
     """From float32 projection rows [q heads | k heads (| v heads of ``dv`` values)], plus ``bias`` (float32,
     laid out like a row) when given: q and k heads normalised per head
     (x * rsqrt(mean x^2 + eps) * weight, the weight of ``hd`` values shared by the heads; no weights: as
@@ -950,7 +959,11 @@ def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, r
     With ``kv`` (the layer's view of its cache pages) k and v also go to each token's row of its page.
     ``pitch`` > 0: every head of ``qkv`` and every row of the cache holds that many elements (at least ``hd`` and
     ``dv``), zeros behind its own.  ``whole_norm``: q (and k) are normalised over the token's whole projection, all
-    heads at once, and the weights hold ``nq * hd`` and ``nkv * hd`` values."""
+    heads at once, and the weights hold ``nq * hd`` and ``nkv * hd`` values.  ``table`` (float32 [T, rot_dim / 2,
+    2]): the step's cosines and sines, taken instead of working them out from ``inv_freq``."""
+    if table is not None and (tuple(table.shape) != (proj.shape[0], rot_dim // 2, 2) or table.dtype != torch.float32
+                              or not table.is_contiguous()):
+        raise KernelError(f"qk_norm_rope_store: a table of cosines and sines [{proj.shape[0]}, {rot_dim // 2}, 2]")
     T = proj.shape[0]
     dv = dv or hd
     pk, pv = (pitch, pitch) if pitch else (hd, dv)
@@ -985,7 +998,8 @@ def qk_norm_rope_store(qkv, proj, batch, nq: int, nkv: int, hd: int, inv_freq, r
         c_float(magnitude), c_int(1 if v_from_k else 0),
         _ptr(batch.positions, "positions", torch.int32), _ptr(batch.seq_of_token, "seq_of_token", torch.int32),
         _ptr(batch.slots, "slots", torch.int32), _ptr(batch.len_after, "len_after", torch.int32),
-        _ptr(inv_freq, "inv_freq", torch.float32), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(dv), c_int(rot_dim),
+        _ptr(inv_freq, "inv_freq", torch.float32), _ptr(table, "table", torch.float32, allow_none=True),
+        c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(dv), c_int(rot_dim),
         c_int(PAIRINGS[pairing]), _ptr(kc, allow_none=True), _ptr(vc, allow_none=True),
         _ptr(pt, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring), c_int(pitch),
         c_int(1 if whole_norm else 0), _stream()))
@@ -1210,7 +1224,7 @@ def conv_rows(u, proj, off_x: int, bx, cw, cb, state, batch) -> None:
 
 def gate_rows(decay, inp, u, wa, wi, ba, bi, rate) -> None:
     """With the channels of u (float32 [T, width]) in ``blocks`` equal parts and wa, wi [blocks, out, in]:
-    r = sigmoid(wa_b u_b + ba), i = sigmoid(wi_b u_b + bi), decay = exp(-rate r), inp = sqrt(1 - decay^2) i u
+    r = sigmoid(wa_b u_b + ba), i = sigmoid(wi_b u_b + bi), a = exp(-rate r), decay = 1 - a, inp = sqrt(1 - a^2) i u
     (all float32 [T, width]; the weights may be of the compute dtype, the sums are 32-bit)."""
     T, width = u.shape
     blocks, bw = wa.shape[0], wa.shape[1]
@@ -1228,7 +1242,7 @@ def gate_rows(decay, inp, u, wa, wi, ba, bi, rate) -> None:
 
 
 def decay_scan(out, decay, inp, proj, off_y: int, off_x: int, by, bx, state, batch) -> None:
-    """S <- decay S + inp token after token from row 0 of the sequence's ``state`` (float32 [slots, taps, width];
+    """S <- S - decay S + inp (``decay`` = 1 - a) token after token from row 0 of the sequence's ``state`` (float32 [slots, taps, width];
     left updated, with the last taps - 1 values of section ``off_x`` + bx in the rows behind it);
     out = S * gelu_tanh(section ``off_y`` of the projection rows + by)."""
     T, width = out.shape

@@ -252,7 +252,8 @@ class Attention(Mixer):
             eps=float(self.qk_norm["eps"]) if self.qk_norm is not None else 0.0,
             v_from_k=self.v_from_k, kv=view.kv if view.writes else None, bias=self.bias,
             norm_after=self.norm_after, magnitude=rope.magnitude if rope is not None else 1.0, dv=self.dv,
-            pitch=self.pad, whole_norm=self.norm_whole)
+            pitch=self.pad, whole_norm=self.norm_whole,
+            table=rope.precise_table(batch) if rope is not None else None)
         gate = None
         if self.gate_name:
             at = (nq + nkv) * hd + (0 if self.v_from_k else nkv * self.dv)

@@ -33,7 +33,9 @@ from .base import PositionEncoding, register_part
 @register_part("position", "rope")
 class Rope(PositionEncoding):
     """Parameters: ``theta``, ``rotary_dim``, ``pairing``; optional ``scaling``: {``factor``, ``original``,
-    ``fast``, ``slow``}, or {``kind``: "wavelength", ``factor``, ``low``, ``high``, ``original``}."""
+    ``fast``, ``slow``}, or {``kind``: "wavelength", ``factor``, ``low``, ``high``, ``original``}; optional
+    ``precise_angles`` (default false): a mixer that packs its projection takes the cosines and sines from a
+    table of the step that is made from 64-bit frequencies with 64-bit angles (once per step for all layers)."""
     graph_safe = True
 
 
@@ -80,10 +82,25 @@ class Rope(PositionEncoding):
             inv = inv / factor * ramp + inv * (1.0 - ramp)
             self.magnitude = 0.1 * math.log(factor) + 1.0
         self._inv_freq_host = inv.to(torch.float32)
-        self.inv_freq = None
+        self._inv_freq64_host = inv
+        self.precise = bool(self.params.get("precise_angles", False))
+        self._table_key = ("rope_table64", inv.numpy().tobytes())
+        self.inv_freq = self.inv_freq64 = None
 
     def load(self, weights):
         self.inv_freq = self._inv_freq_host.to(self.ctx.device)
+        if self.precise:
+            self.inv_freq64 = self._inv_freq64_host.to(self.ctx.device)
+
+    def precise_table(self, batch):
+        """None, or with ``precise_angles`` float32 [T, rotary_dim / 2, 2] of (cos, sin) from 64-bit angles,
+        made once per pass (kept in ``batch.aux``)."""
+        if not self.precise or self.rotary_dim == 0:
+            return None
+        key = self._table_key           # (by the frequencies' values: layers that rotate alike share the table)
+        if key not in batch.aux:
+            batch.aux[key] = kernels.rope_table_precise(batch.positions, self.inv_freq64)
+        return batch.aux[key]
 
     def rotates_half_pairs(self, hd):
         return self.pairing == "half" and self.rotary_dim == hd and self.magnitude == 1.0
