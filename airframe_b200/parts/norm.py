@@ -72,9 +72,8 @@ class RmsNorm(Norm):
             if alias:
                 return x
             return y if fused else then.forward(x, out_dtype)
-        n_parts = 1
-        if isinstance(a, PartialSums):
-            n_parts, a = a.parts.shape[0], a.parts
+        a = terms[0][0]                 # (one term with a scale of 1, whatever form it came in)
+        n_parts = a.shape[0] if a.dim() == 3 else 1
         if then is not None and not (isinstance(then, RmsNorm) and then.offset == self.offset):
             kernels.add_rmsnorm(x, a, self.w, self.eps, self.offset, n_parts=n_parts)
             return then.forward(x, out_dtype)

@@ -31,6 +31,8 @@ the model's parts (``Model.decode_bytes``, ``Model.prefill_flops``).
 for Fiferax and one for Gemma-2 of equal width, depth, feed-forward and vocabulary: prefill of one prompt of
 2,048 tokens, decode at batch 8 after such prompts, and the device time of every kernel of both.
 ``--banitar all|w1024|w2304|w4096|w4096-192`` does the same for Banitar.
+``--zatasun all|w1024|w2304|w4096`` does the same for Zatasun (attention beside a gated linear recurrence in
+every layer, dense and routed feed-forwards in turn).
 """
 from __future__ import annotations
 
@@ -524,6 +526,43 @@ def banitar_points(args) -> None:
     side_by_side(args, args.banitar, BANITAR_POINTS, _banitar_sizes, "banitar")
 
 
+def _zatasun_sizes(width, layers, heads, kv_heads, attn_dim, rec_width, blocks, conv, ff, experts, top, expert_ff,
+                   shared_ff, vocab):
+    """A Zatasun model of `layers` layers (attention with a sink beside a gated linear recurrence in each; a dense
+    feed-forward in the even layers, routed experts with a shared one in the odd ones: `top` experts of
+    `expert_ff` and the shared one of `shared_ff` together read as much as the dense one), and the Gemma-2 model
+    of the same width, depth, heads, feed-forward and vocabulary."""
+    mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": attn_dim, "vdim": attn_dim, "scale": attn_dim ** -0.5,
+                      "rot": {"base": 500000.0, "dims": attn_dim,
+                              "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+             "left_scale": 1.0, "right": {"width": rec_width, "blocks": blocks, "conv": conv}, "right_scale": 1.0}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": {"experts": experts, "top": top},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    zt = {"architecture": "Zatasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+          "layers": [{"type": "parallel", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff} if i % 2 == 0 else moe}
+                     for i in range(layers)]}
+    gemma = dict(GEMMA2_2B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                 num_key_value_heads=kv_heads, head_dim=attn_dim, intermediate_size=ff, vocab_size=vocab,
+                 sliding_window=4096, query_pre_attn_scalar=attn_dim)
+    return zt, gemma
+
+
+ZATASUN_POINTS = {
+    "w1024": dict(width=1024, layers=8, heads=16, kv_heads=4, attn_dim=64, rec_width=1024, blocks=8, conv=4, ff=4096,
+                  experts=16, top=2, expert_ff=1024, shared_ff=2048, vocab=32000),
+    "w2304": dict(width=2304, layers=8, heads=18, kv_heads=6, attn_dim=128, rec_width=2304, blocks=9, conv=4, ff=9216,
+                  experts=16, top=2, expert_ff=2304, shared_ff=4608, vocab=32000),
+    "w4096": dict(width=4096, layers=8, heads=32, kv_heads=8, attn_dim=128, rec_width=4096, blocks=16, conv=4, ff=14336,
+                  experts=32, top=4, expert_ff=2048, shared_ff=6144, vocab=32000),
+}
+
+
+def zatasun_points(args) -> None:
+    """The same figures for Zatasun beside the Gemma-2 model of equal width, depth, heads, feed-forward and
+    vocabulary."""
+    side_by_side(args, args.zatasun, ZATASUN_POINTS, _zatasun_sizes, "zatasun")
+
+
 def side_by_side(args, which, points, make, arm_name) -> None:
     """Prefill and decode of a design at the named points, each beside the Gemma-2 model that `make` pairs it
     with.  One JSON line a model."""
@@ -644,6 +683,8 @@ def main() -> int:
                          "size, then exit (not the default run)")
     ap.add_argument("--banitar", default="", choices=["", "all", *sorted(BANITAR_POINTS)],
                     help="the same for Banitar (not the default run)")
+    ap.add_argument("--zatasun", default="", choices=["", "all", *sorted(ZATASUN_POINTS)],
+                    help="the same for Zatasun (not the default run)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -661,6 +702,9 @@ def main() -> int:
         return 0
     if args.banitar:
         banitar_points(args)
+        return 0
+    if args.zatasun:
+        zatasun_points(args)
         return 0
     line = run_ours(args)
     if line is not None:

@@ -166,12 +166,16 @@ def clamped_expert(h, W, p, limit):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ W[p + "down"].T
 
 
-def routed_ff(h, W, p, mlp):
+def routed_ff(h, W, p, mlp, margins=None):
     """Sigmoid scores from the router; the ``top`` largest choose the experts; a chosen expert's score multiplies
-    its *input*; a shared expert runs for every token and is added times sigmoid(W_sg h)."""
+    its *input*; a shared expert runs for every token and is added times sigmoid(W_sg h).  ``margins`` (a list)
+    receives, per token, by how much the last chosen score exceeds the first one left out."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     s = sigmoid(h @ W[p + "router"].T)
     out = torch.zeros_like(h)
+    if margins is not None:
+        ranked = s.sort(dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < E else torch.full_like(s[:, 0], float("inf")))
     for t in range(h.shape[0]):
         order = sorted(range(E), key=lambda e: (-float(s[t, e]), e))[:top]
         for e in order:
@@ -184,7 +188,7 @@ def routed_ff(h, W, p, mlp):
 
 # ---------------------------------------------------------------- the model
 
-def layer(x, W, i, spec, eps):
+def layer(x, W, i, spec, eps, margins=None):
     p = f"l{i}."
     m = spec["mixer"]
     mixed = (m["left_scale"] * whole_norm_attention(x, W, p + "mix.left.", m["left"], eps)
@@ -193,17 +197,45 @@ def layer(x, W, i, spec, eps):
     mlp = spec["mlp"]
     if mlp is None:
         return x
-    f = dense_ff(x, W, p + "mlp.") if mlp["kind"] == "dense" else routed_ff(x, W, p + "mlp.", mlp)
+    f = dense_ff(x, W, p + "mlp.") if mlp["kind"] == "dense" else routed_ff(x, W, p + "mlp.", mlp, margins)
     return x + rms(f, eps, W[p + "norm2"])
 
 
-def forward(cfg, W, tokens, return_layers=False):
+def forward(cfg, W, tokens, return_layers=False, margins=None):
     """Logits [T, vocab] of one sequence (float64), and with ``return_layers`` the residual stream after every layer."""
     eps = cfg["norm"]["eps"]
     x = rms(W["embed"][torch.as_tensor(tokens, dtype=torch.long)], eps, W["embed.norm"])
     seen = []
     for i, spec in enumerate(cfg["layers"]):
-        x = layer(x, W, i, spec, eps)
+        x = layer(x, W, i, spec, eps, margins)
         seen.append(x.clone())
     logits = (rms(x, eps, W["final.norm"]) @ W["embed"].T) * cfg["logit_scale"]
     return (logits, torch.stack(seen)) if return_layers else logits
+
+
+def logits(cfg, W, tokens):
+    return forward(cfg, W, tokens)
+
+
+def routing_margins(cfg, W, tokens):
+    """Per token, the smallest margin by which any of its routers chose (infinite without a choice to make):
+    where it is tiny, a computation in fewer bits may choose otherwise and still be right."""
+    seen = []
+    forward(cfg, W, tokens, margins=seen)
+    return torch.stack(seen).min(0).values if seen else torch.full((len(tokens),), float("inf"), dtype=F64)
+
+
+def hidden_states(cfg, W, tokens, per_layer):
+    """Appends the residual stream after every layer to ``per_layer``."""
+    _, seen = forward(cfg, W, tokens, return_layers=True)
+    per_layer.extend(seen)
+
+
+def generate_greedy(cfg, W, prompt, n):
+    ids = list(prompt)
+    out = []
+    for _ in range(n):
+        nxt = int(forward(cfg, W, ids)[-1].argmax())
+        out.append(nxt)
+        ids.append(nxt)
+    return out
