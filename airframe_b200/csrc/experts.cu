@@ -76,7 +76,7 @@ AF_EXPORT int af_expert_route(int* ids, float* wts, float* shared_gate, const vo
 // One block.  plan: [0] tiles in use; then per tile (expert, first sorted row, rows).  perm[sorted row] = pair.
 __global__ void __launch_bounds__(1024)
 expert_plan_kernel(int* __restrict__ perm, int* __restrict__ plan, const int* __restrict__ ids, int n_pairs,
-                   int n_experts, int max_tiles) {
+                   int n_experts, int max_tiles, int tile) {
   pdl_launch_dependents();
   extern __shared__ int sh[];                       // count[E], first[E], cursor[E]
   int* count = sh;
@@ -95,10 +95,14 @@ expert_plan_kernel(int* __restrict__ perm, int* __restrict__ plan, const int* __
     int rows = 0, tiles = 0;
     for (int e = 0; e < n_experts; ++e) {
       first[e] = rows;
-      for (int r = 0; r < count[e] && tiles < max_tiles; r += AF_EX_TM, ++tiles) {
+      // an expert's rows in as few tiles as hold them, of equal size (a last tile of a few rows costs a wide
+      // tile's set-up for nothing)
+      const int n_t = (count[e] + tile - 1) / tile;
+      const int per = n_t > 0 ? (count[e] + n_t - 1) / n_t : 0;
+      for (int r = 0; r < count[e] && tiles < max_tiles; r += per, ++tiles) {
         plan[1 + 3 * tiles] = e;
         plan[2 + 3 * tiles] = rows + r;
-        plan[3 + 3 * tiles] = min(AF_EX_TM, count[e] - r);
+        plan[3 + 3 * tiles] = min(per, count[e] - r);
       }
       rows += count[e];
     }
@@ -112,15 +116,50 @@ expert_plan_kernel(int* __restrict__ perm, int* __restrict__ plan, const int* __
 }
 
 AF_EXPORT int af_expert_plan(int* perm, int* plan, const int* ids, int n_pairs, int n_experts, int max_tiles,
-                             cudaStream_t stream) {
+                             int tile, cudaStream_t stream) {
   if (n_pairs == 0) return 0;
-  AF_REQUIRE(n_pairs > 0 && n_experts > 0 && n_experts <= 4096, "af_expert_plan: bad sizes");
+  AF_REQUIRE(n_pairs > 0 && n_experts > 0 && n_experts <= 4096 && tile > 0, "af_expert_plan: bad sizes");
   // (every expert may end on a tile that is not full)
-  AF_REQUIRE(max_tiles >= n_pairs / AF_EX_TM + n_experts || max_tiles >= n_pairs,
+  AF_REQUIRE(max_tiles >= n_pairs / tile + n_experts || max_tiles >= n_pairs,
              "af_expert_plan: room for %d tiles is too little", max_tiles);
   af_launch(expert_plan_kernel, dim3(1), dim3(1024), (size_t)3 * n_experts * sizeof(int), stream, perm, plan, ids,
-            n_pairs, n_experts, max_tiles);
+            n_pairs, n_experts, max_tiles, tile);
   AF_CHECK_LAUNCH("af_expert_plan");
+}
+
+// ---------------------------------------------------------------- the tokens' rows in sorted order
+
+// out[sorted row] = x[perm[sorted row] / top]: the rows a tensor-core product fetches tile by tile.
+template <typename T>
+__global__ void __launch_bounds__(256)
+expert_gather_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ perm, int n_rows, int top,
+                     int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * warps + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const int pair = __ldcg(perm + r);
+  if (!AF_INDEX_OK(pair >= 0 && pair < n_rows, pair)) return;
+  const T* src = x + (size_t)(pair / top) * H;
+  T* dst = out + (size_t)r * H;
+  if ((H * sizeof(T)) % 16 == 0) {
+    const int n16 = H * sizeof(T) / 16;
+    for (int i = lane; i < n16; i += 32) reinterpret_cast<int4*>(dst)[i] = __ldcg(reinterpret_cast<const int4*>(src) + i);
+  } else {
+    for (int i = lane; i < H; i += 32) dst[i] = src[i];
+  }
+}
+
+AF_EXPORT int af_expert_gather(void* out, const void* x, int dtype, const int* perm, int n_rows, int top, int H,
+                               cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AF_REQUIRE(n_rows > 0 && top >= 1 && H > 0 && perm != nullptr, "af_expert_gather: bad sizes");
+  AF_REQUIRE(((uintptr_t)out & 15) == 0 && ((uintptr_t)x & 15) == 0, "af_expert_gather: rows must be 16-byte aligned");
+  AF_DISPATCH_DTYPE(dtype, T,
+                    af_launch(expert_gather_kernel<T>, dim3((n_rows + 7) / 8), dim3(256), 0, stream, (T*)out,
+                              (const T*)x, perm, n_rows, top, H));
+  AF_CHECK_LAUNCH("af_expert_gather");
 }
 
 // ---------------------------------------------------------------- a tile's rows times its expert's matrices

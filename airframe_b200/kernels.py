@@ -1265,12 +1265,20 @@ def decay_scan(out, decay, inp, proj, off_y: int, off_x: int, by, bx, state, bat
 
 # ---------------------------------------------------------------- routed experts
 
-EXPERT_TILE = 32     # pairs of one expert that a block of the experts' products takes
+EXPERT_TILE = 32     # pairs of one expert that a block of the experts' products on the CUDA cores takes
+EXPERT_TC_TILES = (16, 32, 64, 128, 256)     # row tiles of the products on the tensor cores
 
 
-def expert_max_tiles(n_pairs: int, n_experts: int) -> int:
+def expert_max_tiles(n_pairs: int, n_experts: int, tile: int = EXPERT_TILE) -> int:
     """Room for the tiles of ``n_pairs`` (token, choice) pairs however they fall on the experts."""
-    return min(n_pairs, n_pairs // EXPERT_TILE + n_experts)
+    return min(n_pairs, n_pairs // tile + n_experts)
+
+
+def expert_tc_tile(n_pairs: int, n_experts: int) -> int:
+    """The row tile of the tensor-core products: the smallest that holds an expert's share of the pairs when
+    they fall evenly (an expert with more gets several tiles of equal size)."""
+    share = (n_pairs + n_experts - 1) // n_experts
+    return next((t for t in EXPERT_TC_TILES if t >= share), EXPERT_TC_TILES[-1])
 
 
 def expert_route(ids, wts, shared_gate, h, router, n_experts: int) -> None:
@@ -1291,16 +1299,17 @@ def expert_route(ids, wts, shared_gate, h, router, n_experts: int) -> None:
                                   c_int(top), _stream()))
 
 
-def expert_plan(perm, plan, ids, n_experts: int) -> None:
+def expert_plan(perm, plan, ids, n_experts: int, tile: int = EXPERT_TILE) -> None:
     """The (token, choice) pairs of ``ids`` [T, top] sorted by expert: perm int32 [T * top] (sorted row -> pair),
-    plan int32 [1 + 3 * expert_max_tiles]: tiles in use, then (expert, first sorted row, rows) per tile."""
+    plan int32 [1 + 3 * expert_max_tiles]: tiles in use, then (expert, first sorted row, rows) per tile; a tile
+    holds up to ``tile`` rows, and an expert's tiles are of equal size."""
     n_pairs = ids.numel()
     max_tiles = (plan.numel() - 1) // 3
     if perm.numel() != n_pairs or not (perm.is_contiguous() and plan.is_contiguous() and ids.is_contiguous()):
         raise KernelError("expert_plan: one entry of perm per pair")
     _check(_lib().af_expert_plan(_ptr(perm, "perm", torch.int32), _ptr(plan, "plan", torch.int32),
                                  _ptr(ids, "ids", torch.int32), c_int(n_pairs), c_int(n_experts), c_int(max_tiles),
-                                 _stream()))
+                                 c_int(tile), _stream()))
 
 
 def expert_rows(out, a, w0, w1=None, perm=None, plan=None, pair_weight=None, scale_out=None, n_tokens: int = 0,
@@ -1332,6 +1341,55 @@ def expert_rows(out, a, w0, w1=None, perm=None, plan=None, pair_weight=None, sca
                                  _ptr(scale_out, "scale_out", torch.float32, allow_none=True), c_int(n_rows),
                                  c_int(n_tokens), c_int(top), c_int(max_tiles), c_int(N), c_int(K), c_float(limit),
                                  _stream()))
+
+
+def expert_gather(out, x, perm, top: int) -> None:
+    """out[sorted row] = x[perm[sorted row] // top]: the tokens' rows in the order of the plan."""
+    n_rows, H = out.shape
+    if not (out.is_contiguous() and x.is_contiguous()) or x.shape[1] != H or out.dtype != x.dtype \
+            or perm.numel() != n_rows or x.shape[0] * top != n_rows:
+        raise KernelError("expert_gather: contiguous rows of one size and dtype, one entry of perm a row")
+    _check(_lib().af_expert_gather(_ptr(out), _ptr(x), c_int(dtype_code(x.dtype)), _ptr(perm, "perm", torch.int32),
+                                   c_int(n_rows), c_int(top), c_int(H), _stream()))
+
+
+def expert_rows_tc_supported(a, w0) -> bool:
+    """Whether the tensor-core products take these rows and matrices: bfloat16, contiguous, K a multiple of 8,
+    16-byte aligned."""
+    return (a.dtype == torch.bfloat16 and w0.dtype == torch.bfloat16 and a.is_contiguous() and w0.is_contiguous()
+            and a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and w0.data_ptr() % 16 == 0)
+
+
+def expert_rows_tc(out, a, w0, w1=None, perm=None, plan=None, pair_weight=None, scale_out=None, n_tokens: int = 0,
+                   top: int = 1, limit: float = 0.0, tile: int = 0) -> None:
+    """:func:`expert_rows` on the tcgen05 tensor cores (bfloat16 operands, 32-bit sums in TMEM), with one
+    difference: ``a`` holds the sorted rows themselves also for the first product (:func:`expert_gather`).
+    ``tile``: the row tile the plan was made for (without a plan: chosen here)."""
+    n_rows = n_tokens * top
+    E, N, K = w0.shape
+    if not expert_rows_tc_supported(a, w0) or tuple(a.shape) != (n_rows, K) or not out.is_contiguous():
+        raise KernelError("expert_rows_tc: contiguous bfloat16 rows [rows, K], K a multiple of 8, 16-byte aligned")
+    if w1 is not None:
+        if w1.shape != w0.shape or w1.dtype != w0.dtype or not w1.is_contiguous() or w1.data_ptr() % 16:
+            raise KernelError("expert_rows_tc: gate and up matrices alike")
+        if tuple(out.shape) != (n_rows, N) or out.dtype != torch.bfloat16:
+            raise KernelError(f"expert_rows_tc: out bfloat16 [{n_rows}, {N}]")
+    elif tuple(out.shape) != (top, n_tokens, N) or out.dtype != torch.float32:
+        raise KernelError(f"expert_rows_tc: out float32 [{top}, {n_tokens}, {N}]")
+    if plan is None:
+        if E != 1:
+            raise KernelError("expert_rows_tc: several experts need a plan")
+        tile = expert_tc_tile(n_rows, 1)
+    if tile not in EXPERT_TC_TILES:
+        raise KernelError(f"expert_rows_tc: a row tile of {tile}")
+    max_tiles = (plan.numel() - 1) // 3 if plan is not None else 0
+    _check(_lib().af_expert_rows_tc(_ptr(out), _ptr(a), _ptr(w0), _ptr(w1, allow_none=True), c_int(E),
+                                    _ptr(perm, "perm", torch.int32, allow_none=True),
+                                    _ptr(plan, "plan", torch.int32, allow_none=True),
+                                    _ptr(pair_weight, "pair_weight", torch.float32, allow_none=True),
+                                    _ptr(scale_out, "scale_out", torch.float32, allow_none=True), c_int(n_rows),
+                                    c_int(n_tokens), c_int(top), c_int(max_tiles), c_int(tile), c_int(N), c_int(K),
+                                    c_float(limit), _ptr(error_word(a.device), "err", torch.int32), _stream()))
 
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -164,21 +164,32 @@ class RoutedExperts(FeedForward):
         wts = torch.empty(T, top, dtype=torch.float32, device=dev)
         mix = torch.empty(T, dtype=torch.float32, device=dev) if self.shared is not None else None
         kernels.expert_route(ids, wts, mix, x, self.router, self.n_experts)
+        # bfloat16 with sizes the tensor-core products take: the rows in sorted order, then grouped products;
+        # else the products on the CUDA cores (32-bit, or odd sizes), which fetch their rows themselves
+        fast = (kernels.expert_rows_tc_supported(x, self.w_gate) and self.inter % 8 == 0)
+        tile = kernels.expert_tc_tile(T * top, self.n_experts) if fast else kernels.EXPERT_TILE
         perm = torch.empty(T * top, dtype=torch.int32, device=dev)
-        plan = torch.empty(1 + 3 * kernels.expert_max_tiles(T * top, self.n_experts), dtype=torch.int32, device=dev)
-        kernels.expert_plan(perm, plan, ids, self.n_experts)
+        plan = torch.empty(1 + 3 * kernels.expert_max_tiles(T * top, self.n_experts, tile), dtype=torch.int32, device=dev)
+        kernels.expert_plan(perm, plan, ids, self.n_experts, tile)
         mid = torch.empty(T * top, self.inter, dtype=x.dtype, device=dev)
-        kernels.expert_rows(mid, x, self.w_gate, self.w_up, perm=perm, plan=plan, pair_weight=wts, n_tokens=T, top=top,
-                            limit=self.limit)
         out = torch.empty(top, T, self.hidden, dtype=torch.float32, device=dev)
-        kernels.expert_rows(out, mid, self.w_down, perm=perm, plan=plan, n_tokens=T, top=top)
+        if fast:
+            rows = torch.empty(T * top, self.hidden, dtype=x.dtype, device=dev)
+            kernels.expert_gather(rows, x, perm, top)
+            kernels.expert_rows_tc(mid, rows, self.w_gate, self.w_up, perm=perm, plan=plan, pair_weight=wts, n_tokens=T,
+                                   top=top, limit=self.limit, tile=tile)
+            kernels.expert_rows_tc(out, mid, self.w_down, perm=perm, plan=plan, n_tokens=T, top=top, tile=tile)
+        else:
+            kernels.expert_rows(mid, x, self.w_gate, self.w_up, perm=perm, plan=plan, pair_weight=wts, n_tokens=T,
+                                top=top, limit=self.limit)
+            kernels.expert_rows(out, mid, self.w_down, perm=perm, plan=plan, n_tokens=T, top=top)
         terms = [(PartialSums(out), 1.0)]
         if self.shared is not None:
             sf = int(self.shared["intermediate_size"])
             smid = torch.empty(T, sf, dtype=x.dtype, device=dev)
-            kernels.expert_rows(smid, x, self.s_gate, self.s_up, scale_out=mix, n_tokens=T, top=1,
-                                limit=float(self.shared["limit"]))
             sout = torch.empty(1, T, self.hidden, dtype=torch.float32, device=dev)
-            kernels.expert_rows(sout, smid, self.s_down, n_tokens=T, top=1)
+            rows_fn = kernels.expert_rows_tc if fast and sf % 8 == 0 else kernels.expert_rows
+            rows_fn(smid, x, self.s_gate, self.s_up, scale_out=mix, n_tokens=T, top=1, limit=float(self.shared["limit"]))
+            rows_fn(sout, smid, self.s_down, n_tokens=T, top=1)
             terms.append((sout[0], 1.0))
         return WeightedSum(terms)

@@ -273,3 +273,57 @@ def test_residual_step_norms_a_weighted_sum(K, H):
             K.add_normed_terms(x2, dev_terms, w.to(DEV), 1e-5, y=y)
             close(y, want, tol)
             assert torch.equal(x1, x2)
+
+
+@pytest.mark.parametrize("E,top,H,F,T,limit,tiles", [(5, 2, 72, 40, 50, 1.0, (16, 32)), (8, 1, 128, 64, 300, 2.0, (16, 64, 256)),
+                                                      (3, 3, 56, 16, 7, 0.5, (16,)), (2, 1, 40, 24, 1, 4.0, (16,)),
+                                                      (12, 4, 64, 96, 130, 1.5, (32, 128)), (1, 1, 24, 8, 33, 0.7, (32,)),
+                                                      (4, 2, 320, 200, 700, 1.2, (128, 256)), (16, 2, 256, 136, 8, 3.0, (16,))])
+def test_expert_products_on_the_tensor_cores(K, E, top, H, F, T, limit, tiles):
+    """The grouped products over sorted rows: row tiles of every size (an expert's rows in several tiles, tiles
+    that begin in the middle of a box, the last rows of the last expert), feature tiles that end inside a
+    tile of 128 and reach into the next expert's matrix, K that is no multiple of 64; and one expert without a
+    plan (the shared expert's form, scaled per token)."""
+    W = expert_weights(E, H, F, E * 100 + T, shared=24)
+    h = torch.randn(T, H, generator=torch.Generator().manual_seed(T)).bfloat16().double()
+    mlp = {"router": {"experts": E, "top": top}, "expert": {"limit": limit}}
+    want = plain.routed_ff(h, W, "m.", mlp)
+    x = h.bfloat16().to(DEV)
+    router = torch.cat([W["m.router"], W["m.shared.sg"]]).float().to(DEV)
+    ids = torch.empty(T, top, dtype=torch.int32, device=DEV)
+    wts = torch.empty(T, top, device=DEV)
+    mix = torch.empty(T, device=DEV)
+    K.expert_route(ids, wts, mix, x, router, E)
+    stack = lambda role: torch.stack([W[f"m.e{e}.{role}"] for e in range(E)]).bfloat16().to(DEV).contiguous()
+    wg, wu, wd = stack("gate"), stack("up"), stack("down")
+    assert K.expert_rows_tc_supported(x, wg)
+    for tile in tiles + (K.expert_tc_tile(T * top, E),):
+        perm = torch.empty(T * top, dtype=torch.int32, device=DEV)
+        plan = torch.full((1 + 3 * K.expert_max_tiles(T * top, E, tile),), -1, dtype=torch.int32, device=DEV)
+        K.expert_plan(perm, plan, ids, E, tile)
+        entries = plan.cpu()[1: 1 + 3 * int(plan[0])].view(-1, 3)
+        assert int(entries[:, 2].max()) <= tile and int(entries[:, 2].sum()) == T * top
+        rows = torch.empty(T * top, H, dtype=torch.bfloat16, device=DEV)
+        K.expert_gather(rows, x, perm, top)
+        assert torch.equal(rows, x[(perm.long() // top)])
+        mid = torch.full((T * top, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+        K.expert_rows_tc(mid, rows, wg, wu, perm=perm, plan=plan, pair_weight=wts, n_tokens=T, top=top, limit=limit, tile=tile)
+        out = torch.full((top, T, H), float("nan"), device=DEV)
+        K.expert_rows_tc(out, mid, wd, perm=perm, plan=plan, n_tokens=T, top=top, tile=tile)
+        close(out.sum(0), want, 2e-2)
+        # the same rows on the CUDA cores: the two paths differ by the activation's rounding alone
+        mid2 = torch.empty_like(mid)
+        plan32 = torch.empty(1 + 3 * K.expert_max_tiles(T * top, E), dtype=torch.int32, device=DEV)
+        perm2 = torch.empty_like(perm)
+        K.expert_plan(perm2, plan32, ids, E)
+        K.expert_rows(mid2, x, wg, wu, perm=perm2, plan=plan32, pair_weight=wts, n_tokens=T, top=top, limit=limit)
+        close(mid[perm.long().argsort()], mid2[perm2.long().argsort()], 2e-2)      # (pair by pair: an expert's pairs come in any order)
+    K.check_device_errors(DEV)
+    # one expert, the rows as they are, a scale per token behind the activation
+    sg, su, sd = (W[f"m.shared.{r}"].bfloat16().to(DEV).unsqueeze(0).contiguous() for r in ("gate", "up", "down"))
+    smid = torch.empty(T, 24, dtype=torch.bfloat16, device=DEV)
+    K.expert_rows_tc(smid, x, sg, su, scale_out=mix, n_tokens=T, top=1, limit=0.9)
+    sout = torch.empty(1, T, H, device=DEV)
+    K.expert_rows_tc(sout, smid, sd, n_tokens=T, top=1)
+    close(sout[0], plain.sigmoid(h @ W["m.shared.sg"].T) * plain.clamped_expert(h, W, "m.shared.", 0.9), 2e-2)
+    K.check_device_errors(DEV)
