@@ -674,6 +674,80 @@ add_normed_terms_kernel(float* __restrict__ x, const void* __restrict__ a, int a
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) yr[i] = from_f32<TY>(row[i] * inv2 * (offset_next + w_next[i]));
 }
 
+// The same for rows of up to 8192 values with hidden % 4 == 0: a thread owns NV groups of four values, every load
+// of the terms is issued before the first reduction, and the norms' weights are asked for before the wait for the
+// kernel in front.
+template <typename TY, int NV>
+__global__ void __launch_bounds__(1024)
+add_normed_terms_row_kernel(float* __restrict__ x, const void* __restrict__ a, int a_dtype, int a_parts, float scale_a,
+                            const void* __restrict__ b, int b_dtype, int b_parts, float scale_b, size_t part_stride,
+                            const float* __restrict__ w_post, float eps_post, float offset_post, TY* __restrict__ y,
+                            const float* __restrict__ w_next, float eps_next, float offset_next, int hidden) {
+  pdl_launch_dependents();
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  float wp[NV][4], wn[NV][4], tv[NV][4], xv[NV][4];
+  bool on[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int i = (threadIdx.x + v * blockDim.x) * 4;
+    on[v] = i < hidden;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) wp[v][u] = wn[v][u] = tv[v][u] = xv[v][u] = 0.f;
+    if (on[v]) {
+      const float4 t = *reinterpret_cast<const float4*>(w_post + i);
+      wp[v][0] = t.x, wp[v][1] = t.y, wp[v][2] = t.z, wp[v][3] = t.w;
+      if (y != nullptr && w_next != nullptr) {
+        const float4 n = *reinterpret_cast<const float4*>(w_next + i);
+        wn[v][0] = n.x, wn[v][1] = n.y, wn[v][2] = n.z, wn[v][3] = n.w;
+      }
+    }
+  }
+  pdl_wait();
+  a = pdl_fresh(a);
+  b = pdl_fresh(b);
+  x = pdl_fresh(x);
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    if (!on[v]) continue;
+    const size_t at = (size_t)r * hidden + (threadIdx.x + v * blockDim.x) * 4;
+    const float4 xt = *reinterpret_cast<const float4*>(x + at);
+    xv[v][0] = xt.x, xv[v][1] = xt.y, xv[v][2] = xt.z, xv[v][3] = xt.w;
+    term_group(tv[v], scale_a, a, a_dtype, a_parts, part_stride, at);
+    if (b != nullptr) term_group(tv[v], scale_b, b, b_dtype, b_parts, part_stride, at);
+    ss += tv[v][0] * tv[v][0] + tv[v][1] * tv[v][1] + tv[v][2] * tv[v][2] + tv[v][3] * tv[v][3];
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps_post);
+  float s2 = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    if (!on[v]) continue;
+    const size_t at = (size_t)r * hidden + (threadIdx.x + v * blockDim.x) * 4;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      xv[v][u] += tv[v][u] * inv * (offset_post + wp[v][u]);
+      s2 += xv[v][u] * xv[v][u];
+    }
+    *reinterpret_cast<float4*>(x + at) = make_float4(xv[v][0], xv[v][1], xv[v][2], xv[v][3]);
+  }
+  if (y == nullptr) return;
+  float inv2 = 1.f;
+  if (w_next != nullptr) {
+    s2 = block_sum(s2, scratch);
+    inv2 = rsqrtf(s2 / (float)hidden + eps_next);
+  }
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    if (!on[v]) continue;
+    TY* yr = y + (size_t)r * hidden + (threadIdx.x + v * blockDim.x) * 4;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      yr[u] = from_f32<TY>(w_next != nullptr ? xv[v][u] * inv2 * (offset_next + wn[v][u]) : xv[v][u]);
+  }
+}
+
 AF_EXPORT int af_add_normed_terms(float* x, const void* a, int a_dtype, int a_parts, float scale_a, const void* b,
                                   int b_dtype, int b_parts, float scale_b, const float* w_post, float eps_post,
                                   float offset_post, void* y, int y_dtype, const float* w_next, float eps_next,
@@ -686,6 +760,23 @@ AF_EXPORT int af_add_normed_terms(float* x, const void* a, int a_dtype, int a_pa
              "af_add_normed_terms: partial sums are float");
   AF_REQUIRE((size_t)hidden * sizeof(float) <= 48 * 1024, "af_add_normed_terms: rows of up to 12288 values");
   const size_t part_stride = (size_t)n_rows * hidden;
+  if (hidden % 4 == 0 && hidden <= 8192 &&
+      (((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w_post | (uintptr_t)w_next | (uintptr_t)y) & 15) == 0) {
+    const int nv = hidden > 4096 ? 2 : 1;
+    const int row_threads = ((hidden / (4 * nv) + 31) / 32) * 32;
+    if (nv == 2) {
+      AF_DISPATCH_DTYPE(y_dtype, TY,
+                        af_launch(add_normed_terms_row_kernel<TY, 2>, dim3(n_rows), dim3(row_threads), 0, stream, x, a,
+                                  a_dtype, a_parts, scale_a, b, b_dtype, b_parts, scale_b, part_stride, w_post, eps_post,
+                                  offset_post, (TY*)y, w_next, eps_next, offset_next, hidden));
+    } else {
+      AF_DISPATCH_DTYPE(y_dtype, TY,
+                        af_launch(add_normed_terms_row_kernel<TY, 1>, dim3(n_rows), dim3(row_threads), 0, stream, x, a,
+                                  a_dtype, a_parts, scale_a, b, b_dtype, b_parts, scale_b, part_stride, w_post, eps_post,
+                                  offset_post, (TY*)y, w_next, eps_next, offset_next, hidden));
+    }
+    AF_CHECK_LAUNCH("af_add_normed_terms");
+  }
   const int threads = hidden >= 2048 ? 256 : 128;
   AF_DISPATCH_DTYPE(y_dtype, TY,
                     af_launch(add_normed_terms_kernel<TY>, dim3(n_rows), dim3(threads), (size_t)hidden * sizeof(float),

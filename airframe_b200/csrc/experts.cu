@@ -17,7 +17,22 @@
 // ---------------------------------------------------------------- the router
 
 template <typename TX>
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ void load4_f32(float* v, const TX* p);
+template <>
+__device__ __forceinline__ void load4_f32<float>(float* v, const float* p) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void load4_f32<__nv_bfloat16>(float* v, const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  v[0] = __uint_as_float(raw.x << 16), v[1] = __uint_as_float(raw.x & 0xffff0000u);
+  v[2] = __uint_as_float(raw.y << 16), v[3] = __uint_as_float(raw.y & 0xffff0000u);
+}
+
+// One block per token; a warp per expert at a time.  Few tokens (a decode step) get a warp for every expert.
+template <typename TX>
+__global__ void __launch_bounds__(1024)
 expert_route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ shared_gate,
                     const TX* __restrict__ h, const float* __restrict__ router, int hidden, int n_experts, int top) {
   pdl_launch_dependents();
@@ -28,10 +43,28 @@ expert_route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __res
   pdl_wait();
   h = pdl_fresh(h);
   const TX* x = h + (size_t)t * hidden;
+  const bool vec = hidden % 4 == 0 && (((uintptr_t)h | (uintptr_t)router) & 15) == 0;
   for (int e = warp; e < rows; e += nwarp) {
     const float* w = router + (size_t)e * hidden;
     float z = 0.f;
-    for (int i = lane; i < hidden; i += 32) z = fmaf(w[i], to_f32<TX>(x[i]), z);
+    if (vec) {                                      // four values a lane and load, four loads in flight
+      float zz[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int i0 = lane * 4; i0 < hidden; i0 += 512) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * 128;
+          if (i < hidden) {
+            const float4 wv = *reinterpret_cast<const float4*>(w + i);
+            float xv[4];
+            load4_f32<TX>(xv, x + i);
+            zz[u] = fmaf(wv.x, xv[0], fmaf(wv.y, xv[1], fmaf(wv.z, xv[2], fmaf(wv.w, xv[3], zz[u]))));
+          }
+        }
+      }
+      z = (zz[0] + zz[1]) + (zz[2] + zz[3]);
+    } else {
+      for (int i = lane; i < hidden; i += 32) z = fmaf(w[i], to_f32<TX>(x[i]), z);
+    }
     z = warp_sum(z);
     if (lane == 0) score[e] = 1.f / (1.f + expf(-z));
   }
@@ -65,8 +98,10 @@ AF_EXPORT int af_expert_route(int* ids, float* wts, float* shared_gate, const vo
              "af_expert_route: %d of %d experts", top, n_experts);
   AF_REQUIRE(n_experts <= 8192, "af_expert_route: up to 8192 experts");
   const size_t smem = (size_t)(n_experts + 1) * sizeof(float);
+  const int rows = n_experts + (shared_gate != nullptr ? 1 : 0);
+  const int threads = n_tokens > 1024 ? 128 : (rows >= 32 ? 1024 : rows <= 4 ? 128 : 32 * rows);
   AF_DISPATCH_DTYPE(h_dtype, TX,
-                    af_launch(expert_route_kernel<TX>, dim3(n_tokens), dim3(128), smem, stream, ids, wts, shared_gate,
+                    af_launch(expert_route_kernel<TX>, dim3(n_tokens), dim3(threads), smem, stream, ids, wts, shared_gate,
                               (const TX*)h, router, hidden, n_experts, top));
   AF_CHECK_LAUNCH("af_expert_route");
 }

@@ -17,6 +17,11 @@
 //   warp 1      TMEM allocation, MMA issue (one lane), TMEM release
 //   warps 2..5  epilogue: TMEM -> registers -> global
 //
+// GATES is the same grouped product put to another use: the two gates of a gated linear recurrence, whose
+// matrices are block-diagonal.  An "expert" is a block of channels, every block takes all rows, its columns of
+// the input rows begin at block * K, and the epilogue turns the two sums into what the scan wants:
+//   r = sigmoid(. + ba), i = sigmoid(. + bi), a = exp(-rate r):  decay = 1 - a,  input = sqrt(1 - a^2) i u.
+//
 // A block walks the tiles blockIdx.x, + gridDim.x, ... (feature tile fastest: blocks that run together share a
 // row tile in L2); the number of row tiles is read from the plan on the device, so the host never waits for it.
 // Every wait on an mbarrier is bounded in time; one that runs out sets the error word, lets copies land, frees
@@ -49,7 +54,17 @@ struct ExArgs {
   const float* scale_out;   // DUAL: post per token (null: 1)
   float limit;
   int* err;
+  // GATES only
+  int uniform;              // every expert takes all rows (no plan): row tiles of BN rows, expert by expert
+  float* out2;              // input [rows, experts * N]; out is decay
+  const float* u;           // [rows, experts * N] 32-bit, what the bfloat16 rows were rounded from
+  long long ld_u;           // experts * N
+  const float* ba;
+  const float* bi;
+  const float* rate;
 };
+
+enum { EX_DOWN = 0, EX_ACT = 1, EX_GATES = 2 };
 
 __device__ __forceinline__ float ex_act(float g, float u, float limit) {
   g = fminf(g, limit);
@@ -63,9 +78,14 @@ __device__ __forceinline__ float ex_act(float g, float u, float limit) {
 
 __device__ __forceinline__ void ex_tile(const ExArgs& a, int row_tile, int bn, int* expert, int* row0, int* rows) {
   if (a.plan != nullptr) {
-    *expert = __ldg(a.plan + 1 + 3 * row_tile);
-    *row0 = __ldg(a.plan + 2 + 3 * row_tile);
-    *rows = __ldg(a.plan + 3 + 3 * row_tile);
+    *expert = __ldcg(a.plan + 1 + 3 * row_tile);
+    *row0 = __ldcg(a.plan + 2 + 3 * row_tile);
+    *rows = __ldcg(a.plan + 3 + 3 * row_tile);
+  } else if (a.uniform) {
+    const int per = (a.n_rows + bn - 1) / bn;
+    *expert = row_tile / per;
+    *row0 = (row_tile % per) * bn;
+    *rows = min(bn, a.n_rows - *row0);
   } else {
     *expert = 0;
     *row0 = row_tile * bn;
@@ -73,11 +93,14 @@ __device__ __forceinline__ void ex_tile(const ExArgs& a, int row_tile, int bn, i
   }
 }
 
-template <int BN, bool DUAL>
+template <int BN, int EPI>
 __global__ void __launch_bounds__(EX_THREADS, BN <= 64 ? 2 : 1)
 expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
                       const __grid_constant__ CUtensorMap map_x, ExArgs a) {
+  constexpr bool DUAL = EPI != EX_DOWN;
+  constexpr bool GATES = EPI == EX_GATES;
   constexpr int NACC = DUAL ? 2 : 1;
+  constexpr int XB = BN < 64 ? BN : 64;          // rows of a box of the input rows: a tile fetches as many boxes as hold its rows
   constexpr int STAGES = ex_stages(BN, NACC);
   constexpr int A_BYTES = EX_BM * EX_BK * 2;
   constexpr int STAGE_BYTES = ex_stage_bytes(BN, NACC);
@@ -130,6 +153,8 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_c
         int expert, row0, rows;
         ex_tile(a, tile / a.tiles_w, BN, &expert, &row0, &rows);
         const int w_row = expert * a.N + (tile % a.tiles_w) * EX_BM;
+        const int x_col = GATES ? expert * a.K : 0;
+        const int boxes = (min(rows, BN) + XB - 1) / XB;
         bool ok = true;
         for (int kb = 0; kb < total_kb; ++kb, ++it) {
           const int s = it % STAGES;
@@ -139,11 +164,12 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_c
             break;
           }
           unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
-          mbar_expect_tx(&full[s], STAGE_BYTES);
+          mbar_expect_tx(&full[s], NACC * A_BYTES + boxes * XB * EX_BK * 2);
           const int k = kb * EX_BK;
           tma_load_2d(st, &map_w0, k, w_row, &full[s]);
           if (DUAL) tma_load_2d(st + A_BYTES, &map_w1, k, w_row, &full[s]);
-          tma_load_2d(st + NACC * A_BYTES, &map_x, k, row0, &full[s]);
+          for (int b = 0; b < boxes; ++b)
+            tma_load_2d(st + NACC * A_BYTES + b * XB * EX_BK * 2, &map_x, x_col + k, row0 + b * XB, &full[s]);
         }
         if (!ok) break;
       }
@@ -208,6 +234,34 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_c
           tmem_ld16(lane_base + c0, g);
           if constexpr (DUAL) tmem_ld16(lane_base + BN + c0, u);
         }
+        if constexpr (GATES) {
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (ch == n_chunks - 1) {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty);
+          }
+          if (f < a.N) {
+            const int col = expert * a.N + f;
+            const size_t ldu = (size_t)a.ld_u;
+            const float ab = __ldg(a.ba + col), ib = __ldg(a.bi + col), rt = __ldg(a.rate + col);
+            const int n = min(CW, rows - c0);
+            float uv[CW];
+#pragma unroll
+            for (int j = 0; j < CW; ++j) uv[j] = j < n ? __ldcg(a.u + (size_t)(row0 + c0 + j) * ldu + col) : 0.f;
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+              if (j >= n) continue;
+              const float r = 1.f / (1.f + expf(-(g[j] + ab)));
+              const float i = 1.f / (1.f + expf(-(u[j] + ib)));
+              const float la = -rt * r;                               // log a
+              const size_t at = (size_t)(row0 + c0 + j) * ldu + col;
+              static_cast<float*>(a.out)[at] = -expm1f(la);           // 1 - a
+              a.out2[at] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * i * uv[j];
+            }
+          }
+          continue;
+        }
         // what the chunk's rows need besides the sums: lane l fetches it for row c0 + l
         const int r = c0 + lane;
         int pair = -1;
@@ -259,15 +313,15 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_c
   if (threadIdx.x == 0 && give_up_s && a.err) atomicExch(a.err, 1);
 }
 
-template <int BN, bool DUAL>
+template <int BN, int EPI>
 int ex_launch(const CUtensorMap& m0, const CUtensorMap& m1, const CUtensorMap& mx, const ExArgs& a, cudaStream_t stream) {
-  constexpr int NACC = DUAL ? 2 : 1;
+  constexpr int NACC = EPI != EX_DOWN ? 2 : 1;
   constexpr int smem = ex_stages(BN, NACC) * ex_stage_bytes(BN, NACC) + 1024;
   static bool configured[AF_MAX_DEVICES] = {};
   const int dev = af_current_device();
   if (dev < 0) return -1;
   if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(expert_rows_tc_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(expert_rows_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return af_fail((int)e, "expert_rows_tc: %s", cudaGetErrorString(e));
     configured[dev] = true;
   }
@@ -275,19 +329,19 @@ int ex_launch(const CUtensorMap& m0, const CUtensorMap& m1, const CUtensorMap& m
   if (sms <= 0) return -1;
   const long long tiles = (long long)a.max_row_tiles * a.tiles_w;
   const long long most = BN <= 64 ? tiles : (tiles < sms ? tiles : sms);   // few rows: a block per tile
-  af_launch(expert_rows_tc_kernel<BN, DUAL>, dim3((unsigned)most), dim3(EX_THREADS), smem, stream, m0, m1, mx, a);
+  af_launch(expert_rows_tc_kernel<BN, EPI>, dim3((unsigned)most), dim3(EX_THREADS), smem, stream, m0, m1, mx, a);
   AF_CHECK_LAUNCH("af_expert_rows_tc");
 }
 
-template <bool DUAL>
+template <int EPI>
 int ex_launch_bn(int bn, const CUtensorMap& m0, const CUtensorMap& m1, const CUtensorMap& mx, const ExArgs& a,
                  cudaStream_t s) {
   switch (bn) {
-    case 16: return ex_launch<16, DUAL>(m0, m1, mx, a, s);
-    case 32: return ex_launch<32, DUAL>(m0, m1, mx, a, s);
-    case 64: return ex_launch<64, DUAL>(m0, m1, mx, a, s);
-    case 128: return ex_launch<128, DUAL>(m0, m1, mx, a, s);
-    case 256: return ex_launch<256, DUAL>(m0, m1, mx, a, s);
+    case 16: return ex_launch<16, EPI>(m0, m1, mx, a, s);
+    case 32: return ex_launch<32, EPI>(m0, m1, mx, a, s);
+    case 64: return ex_launch<64, EPI>(m0, m1, mx, a, s);
+    case 128: return ex_launch<128, EPI>(m0, m1, mx, a, s);
+    case 256: return ex_launch<256, EPI>(m0, m1, mx, a, s);
   }
   return af_fail(-1, "af_expert_rows_tc: row tile %d", bn);
 }
@@ -316,11 +370,43 @@ AF_EXPORT int af_expert_rows_tc(void* out, const void* a, const void* w0, const 
   if (rc) return rc;
   rc = af_make_map_bf16(&m1, w1 != nullptr ? w1 : w0, (long long)n_experts * N, K, K, EX_BM);
   if (rc) return rc;
-  rc = af_make_map_bf16(&mx, a, n_rows, K, K, tile);
+  rc = af_make_map_bf16(&mx, a, n_rows, K, K, tile < 64 ? tile : 64);
   if (rc) return rc;
   ExArgs args{out, N, K, n_rows, n_tokens, top, (N + EX_BM - 1) / EX_BM,
               plan != nullptr ? max_tiles : (n_rows + tile - 1) / tile, perm, plan, pair_weight, scale_out, limit, err};
   AF_REQUIRE(args.max_row_tiles > 0, "af_expert_rows_tc: no tiles");
-  if (w1 != nullptr) return ex_launch_bn<true>(tile, m0, m1, mx, args, stream);
-  return ex_launch_bn<false>(tile, m0, m1, mx, args, stream);
+  if (w1 != nullptr) return ex_launch_bn<EX_ACT>(tile, m0, m1, mx, args, stream);
+  return ex_launch_bn<EX_DOWN>(tile, m0, m1, mx, args, stream);
+}
+
+// The gates of a gated linear recurrence on the tensor cores: with the channels in `blocks` equal parts of bw,
+// u16 [n_rows, blocks * bw] bfloat16 (the rounding of u), wa, wi [blocks, bw, bw] bfloat16 ([out, in]):
+//   r = sigmoid(wa_b u_b + ba), i = sigmoid(wi_b u_b + bi), a = exp(-rate r), decay = 1 - a, input = sqrt(1 - a^2) i u
+// with the sums in 32 bits and everything behind them in 32 bits from the 32-bit u.  bw a multiple of 8.
+AF_EXPORT int af_gate_rows_tc(float* decay, float* input, const float* u, const void* u16, const void* wa, const void* wi,
+                              const float* ba, const float* bi, const float* rate, int n_rows, int blocks, int bw,
+                              int* err, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AF_REQUIRE(n_rows > 0 && blocks > 0 && bw > 0 && bw % 8 == 0, "af_gate_rows_tc: %d blocks of %d channels", blocks, bw);
+  AF_REQUIRE(((uintptr_t)u16 & 15) == 0 && ((uintptr_t)wa & 15) == 0 && ((uintptr_t)wi & 15) == 0,
+             "af_gate_rows_tc: operands must be 16-byte aligned");
+  const int tile = n_rows <= 16 ? 16 : n_rows <= 32 ? 32 : n_rows <= 64 ? 64 : n_rows <= 128 ? 128 : 256;
+  const long long width = (long long)blocks * bw;
+  CUtensorMap m0, m1, mx;
+  int rc = af_make_map_bf16(&m0, wa, width, bw, bw, EX_BM);
+  if (rc) return rc;
+  rc = af_make_map_bf16(&m1, wi, width, bw, bw, EX_BM);
+  if (rc) return rc;
+  rc = af_make_map_bf16(&mx, u16, n_rows, width, width, tile < 64 ? tile : 64);
+  if (rc) return rc;
+  ExArgs args{decay, bw, bw, n_rows, n_rows, 1, (bw + EX_BM - 1) / EX_BM, blocks * ((n_rows + tile - 1) / tile),
+              nullptr, nullptr, nullptr, nullptr, 0.f, err};
+  args.uniform = 1;
+  args.out2 = input;
+  args.u = u;
+  args.ld_u = width;
+  args.ba = ba;
+  args.bi = bi;
+  args.rate = rate;
+  return ex_launch_bn<EX_GATES>(tile, m0, m1, mx, args, stream);
 }

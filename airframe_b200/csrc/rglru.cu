@@ -17,7 +17,7 @@
 // ---------------------------------------------------------------- the convolution
 
 __global__ void __launch_bounds__(256)
-conv_rows_kernel(float* __restrict__ u, const float* __restrict__ proj, long long ld, int off_x,
+conv_rows_kernel(float* __restrict__ u, __nv_bfloat16* __restrict__ u16, const float* __restrict__ proj, long long ld, int off_x,
                  const float* __restrict__ bx, const float* __restrict__ cw, const float* __restrict__ cb,
                  const float* __restrict__ state, const int* __restrict__ seq_of_token,
                  const int* __restrict__ seq_starts, const int* __restrict__ slots, int n_tokens, int width, int taps) {
@@ -45,16 +45,17 @@ conv_rows_kernel(float* __restrict__ u, const float* __restrict__ proj, long lon
     acc += cw[(size_t)c * taps + k] * v;
   }
   u[i] = acc;
+  if (u16 != nullptr) u16[i] = __float2bfloat16_rn(acc);      // (what a tensor-core product of the gates reads)
 }
 
-AF_EXPORT int af_conv_rows(float* u, const float* proj, long long ld, int off_x, const float* bx, const float* cw,
+AF_EXPORT int af_conv_rows(float* u, void* u16, const float* proj, long long ld, int off_x, const float* bx, const float* cw,
                            const float* cb, const float* state, const int* seq_of_token, const int* seq_starts,
                            const int* slots, int n_tokens, int width, int taps, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   AF_REQUIRE(n_tokens > 0 && width > 0 && taps >= 1, "af_conv_rows: bad sizes");
   const size_t blocks = ((size_t)n_tokens * width + 255) / 256;
   AF_REQUIRE(blocks < (1ull << 31), "af_conv_rows: too many rows");
-  af_launch(conv_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, u, proj, ld, off_x, bx, cw, cb, state,
+  af_launch(conv_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, u, (__nv_bfloat16*)u16, proj, ld, off_x, bx, cw, cb, state,
             seq_of_token, seq_starts, slots, n_tokens, width, taps);
   AF_CHECK_LAUNCH("af_conv_rows");
 }
@@ -125,6 +126,82 @@ gate_rows_kernel(float* __restrict__ decay, float* __restrict__ input, const flo
   }
 }
 
+// Few tokens (a decode step): a warp owns one output of both gates for eight tokens, whose u of this block of
+// channels waits in shared memory; a lane reads eight weights of each matrix at a time.  Every output adds its
+// products in an order that depends on nothing else in the step.
+#define AF_GF_TM 8
+template <typename TW>
+__device__ __forceinline__ void load8_f32(float* v, const TW* p);
+template <>
+__device__ __forceinline__ void load8_f32<float>(float* v, const float* p) {
+  const float4 t0 = *reinterpret_cast<const float4*>(p), t1 = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = t0.x, v[1] = t0.y, v[2] = t0.z, v[3] = t0.w, v[4] = t1.x, v[5] = t1.y, v[6] = t1.z, v[7] = t1.w;
+}
+template <>
+__device__ __forceinline__ void load8_f32<__nv_bfloat16>(float* v, const __nv_bfloat16* p) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const unsigned r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[2 * j] = __uint_as_float(r[j] << 16), v[2 * j + 1] = __uint_as_float(r[j] & 0xffff0000u);
+}
+
+template <typename TW>
+__global__ void __launch_bounds__(256)
+gate_rows_few_kernel(float* __restrict__ decay, float* __restrict__ input, const float* __restrict__ u,
+                     const TW* __restrict__ wa, const TW* __restrict__ wi, const float* __restrict__ ba,
+                     const float* __restrict__ bi, const float* __restrict__ rate, int n_tokens, int width, int bw) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) float uf[];               // [AF_GF_TM][bw]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.x * 8 + warp, b = blockIdx.y, t0 = blockIdx.z * AF_GF_TM;
+  const bool mine = n < bw;
+  const TW* war = wa + ((size_t)b * bw + (mine ? n : 0)) * bw;
+  const TW* wir = wi + ((size_t)b * bw + (mine ? n : 0)) * bw;
+  // (the weights do not depend on the kernel in front: the first of them are on their way during the wait)
+  float a8[8], g8[8];
+  const int k_first = lane * 8;
+  if (mine && k_first < bw) load8_f32<TW>(a8, war + k_first), load8_f32<TW>(g8, wir + k_first);
+  pdl_wait();
+  u = pdl_fresh(u);
+  for (int e = threadIdx.x * 4; e < AF_GF_TM * bw; e += 1024) {
+    const int m = e / bw, k = e % bw;                       // (bw is a multiple of 8: four values stay in a row)
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (t0 + m < n_tokens) v = *reinterpret_cast<const float4*>(u + (size_t)(t0 + m) * width + (size_t)b * bw + k);
+    *reinterpret_cast<float4*>(uf + e) = v;
+  }
+  __syncthreads();
+  if (!mine) return;
+  float acc_a[AF_GF_TM], acc_i[AF_GF_TM];
+#pragma unroll
+  for (int m = 0; m < AF_GF_TM; ++m) acc_a[m] = acc_i[m] = 0.f;
+  for (int k0 = k_first; k0 < bw; k0 += 256) {
+    if (k0 != k_first) load8_f32<TW>(a8, war + k0), load8_f32<TW>(g8, wir + k0);
+#pragma unroll
+    for (int m = 0; m < AF_GF_TM; ++m) {
+      const float4 v0 = *reinterpret_cast<const float4*>(uf + m * bw + k0);
+      const float4 v1 = *reinterpret_cast<const float4*>(uf + m * bw + k0 + 4);
+      const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc_a[m] = fmaf(a8[j], v[j], acc_a[m]), acc_i[m] = fmaf(g8[j], v[j], acc_i[m]);
+    }
+  }
+  float sa = 0.f, si = 0.f;                                 // lane m keeps token t0 + m's sums
+#pragma unroll
+  for (int m = 0; m < AF_GF_TM; ++m) {
+    const float ta = warp_sum(acc_a[m]), ti = warp_sum(acc_i[m]);
+    if (lane == m) sa = ta, si = ti;
+  }
+  const int t = t0 + lane;
+  if (lane >= AF_GF_TM || t >= n_tokens) return;
+  const int c = b * bw + n;
+  const float r = 1.f / (1.f + expf(-(sa + ba[c])));
+  const float g = 1.f / (1.f + expf(-(si + bi[c])));
+  const float la = -rate[c] * r;                            // log a
+  const size_t at = (size_t)t * width + c;
+  decay[at] = -expm1f(la);                                  // 1 - a
+  input[at] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * g * uf[lane * bw + n];      // sqrt(1 - a^2) i u
+}
+
 AF_EXPORT int af_gate_rows(float* decay, float* input, const float* u, const void* wa, const void* wi, int w_dtype,
                            const float* ba, const float* bi, const float* rate, int n_tokens, int width, int blocks,
                            cudaStream_t stream) {
@@ -132,6 +209,14 @@ AF_EXPORT int af_gate_rows(float* decay, float* input, const float* u, const voi
   AF_REQUIRE(n_tokens > 0 && width > 0 && blocks > 0 && width % blocks == 0,
              "af_gate_rows: %d channels in %d blocks", width, blocks);
   const int bw = width / blocks;
+  if (n_tokens <= 4 * AF_GF_TM && bw % 8 == 0 && (size_t)AF_GF_TM * bw * sizeof(float) <= 48 * 1024 &&
+      (((uintptr_t)u | (uintptr_t)wa | (uintptr_t)wi) & 15) == 0 && blocks < 65536) {
+    const dim3 few((bw + 7) / 8, blocks, (n_tokens + AF_GF_TM - 1) / AF_GF_TM);
+    AF_DISPATCH_DTYPE(w_dtype, TW,
+                      af_launch(gate_rows_few_kernel<TW>, few, dim3(256), (size_t)AF_GF_TM * bw * sizeof(float), stream,
+                                decay, input, u, (const TW*)wa, (const TW*)wi, ba, bi, rate, n_tokens, width, bw));
+    AF_CHECK_LAUNCH("af_gate_rows");
+  }
   const dim3 grid((n_tokens + AF_GR_TM - 1) / AF_GR_TM, blocks, (bw + AF_GR_TN - 1) / AF_GR_TN);
   AF_REQUIRE(grid.y < 65536 && grid.z < 65536, "af_gate_rows: too many blocks of channels");
   AF_DISPATCH_DTYPE(w_dtype, TW,

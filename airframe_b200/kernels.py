@@ -1202,11 +1202,14 @@ def scale_(z, s: float) -> None:
 
 # ---------------------------------------------------------------- a gated linear recurrence with a convolution in front
 
-def conv_rows(u, proj, off_x: int, bx, cw, cb, state, batch) -> None:
+def conv_rows(u, proj, off_x: int, bx, cw, cb, state, batch, u16=None) -> None:
     """u = the causal convolution per channel of (section ``off_x`` of the float32 projection rows + bx), plus
     cb: ``cw`` float32 [width, taps], the last tap on the current token; the tokens before the step come from
-    rows 1 .. taps-1 of the sequence's ``state`` (float32 [slots, taps, width]; zeros for a new sequence)."""
+    rows 1 .. taps-1 of the sequence's ``state`` (float32 [slots, taps, width]; zeros for a new sequence).
+    ``u16`` (bfloat16, like u): also receives u, rounded."""
     T, width = u.shape
+    if u16 is not None and (u16.dtype != torch.bfloat16 or u16.shape != u.shape or not u16.is_contiguous()):
+        raise KernelError("conv_rows: u16 is a contiguous bfloat16 tensor of u's shape")
     taps = cw.shape[1]
     if u.dtype != torch.float32 or not u.is_contiguous() or tuple(cw.shape) != (width, taps) or not cw.is_contiguous():
         raise KernelError(f"conv_rows: u contiguous float32 [T, {width}], taps [{width}, taps]")
@@ -1215,7 +1218,7 @@ def conv_rows(u, proj, off_x: int, bx, cw, cb, state, batch) -> None:
     if off_x + width > proj.shape[1] or bx.numel() != width or cb.numel() != width:
         raise KernelError("conv_rows: the section lies outside the projection row, or a bias of another size")
     pp, ld = _f32_rows(proj, "proj")
-    _check(_lib().af_conv_rows(_ptr(u), pp, ld, c_int(off_x), _ptr(bx, "bx", torch.float32), _ptr(cw, "cw", torch.float32),
+    _check(_lib().af_conv_rows(_ptr(u), _ptr(u16, allow_none=True), pp, ld, c_int(off_x), _ptr(bx, "bx", torch.float32), _ptr(cw, "cw", torch.float32),
                                _ptr(cb, "cb", torch.float32), _ptr(state, "state", torch.float32),
                                _ptr(batch.seq_of_token, "seq_of_token", torch.int32),
                                _ptr(batch.seq_starts, "seq_starts", torch.int32), _ptr(batch.slots, "slots", torch.int32),
@@ -1239,6 +1242,36 @@ def gate_rows(decay, inp, u, wa, wi, ba, bi, rate) -> None:
     _check(_lib().af_gate_rows(_ptr(decay), _ptr(inp), _ptr(u), _ptr(wa), _ptr(wi), c_int(dtype_code(wa.dtype)),
                                _ptr(ba, "ba", torch.float32), _ptr(bi, "bi", torch.float32),
                                _ptr(rate, "rate", torch.float32), c_int(T), c_int(width), c_int(blocks), _stream()))
+
+
+GATE_TC_ROWS = 64     # from so many rows on the gates' products go to the tensor cores
+
+
+def gate_rows_tc_supported(u, wa) -> bool:
+    """Whether :func:`gate_rows_tc` takes these: bfloat16 matrices whose blocks hold a multiple of 8 channels."""
+    return wa.dtype == torch.bfloat16 and wa.shape[1] % 8 == 0 and wa.is_contiguous() and wa.data_ptr() % 16 == 0
+
+
+def gate_rows_tc(decay, inp, u, u16, wa, wi, ba, bi, rate) -> None:
+    """:func:`gate_rows` with the two products on the tcgen05 tensor cores: they read ``u16``, the bfloat16
+    rounding of u (bfloat16 matrices, 32-bit sums); the sigmoids, the decay and the input of the scan are worked
+    out in 32 bits from the sums and the 32-bit u."""
+    T, width = u.shape
+    blocks, bw = wa.shape[0], wa.shape[1]
+    if blocks * bw != width or tuple(wa.shape) != (blocks, bw, bw) or wi.shape != wa.shape or wi.dtype != wa.dtype \
+            or not gate_rows_tc_supported(u, wa) or not wi.is_contiguous() or wi.data_ptr() % 16:
+        raise KernelError(f"gate_rows_tc: bfloat16 gate matrices [blocks, {width} / blocks, {width} / blocks], blocks of a multiple of 8")
+    for t, name in ((decay, "decay"), (inp, "inp"), (u, "u")):
+        if t.dtype != torch.float32 or tuple(t.shape) != (T, width) or not t.is_contiguous():
+            raise KernelError(f"gate_rows_tc: {name} must be contiguous float32 [{T}, {width}]")
+    if u16.dtype != torch.bfloat16 or u16.shape != u.shape or not u16.is_contiguous() or u16.data_ptr() % 16:
+        raise KernelError("gate_rows_tc: u16 is u in bfloat16")
+    if ba.numel() != width or bi.numel() != width or rate.numel() != width:
+        raise KernelError("gate_rows_tc: biases and rates of one value a channel")
+    _check(_lib().af_gate_rows_tc(_ptr(decay), _ptr(inp), _ptr(u), _ptr(u16), _ptr(wa), _ptr(wi),
+                                  _ptr(ba, "ba", torch.float32), _ptr(bi, "bi", torch.float32),
+                                  _ptr(rate, "rate", torch.float32), c_int(T), c_int(blocks), c_int(bw),
+                                  _ptr(error_word(u.device), "err", torch.int32), _stream()))
 
 
 def decay_scan(out, decay, inp, proj, off_y: int, off_x: int, by, bx, state, batch) -> None:

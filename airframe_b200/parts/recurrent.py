@@ -307,10 +307,17 @@ class RgLru(_StateMixer):
         T, w, off, f32 = x.shape[0], self.width, self.off, torch.float32
         proj = linear(x, self.w_in, out_dtype=f32)
         u = torch.empty(T, w, dtype=f32, device=x.device)
-        kernels.conv_rows(u, proj, off["x"], self.x_bias, self.conv_w, self.conv_b, view.state, batch)
+        # many rows in bfloat16: the gates' block-diagonal products on the tensor cores, from u rounded as
+        # every product's input is; few rows (a decode step) or 32-bit: on the CUDA cores from u itself
+        fast = T >= kernels.GATE_TC_ROWS and kernels.gate_rows_tc_supported(u, self.w_a)
+        u16 = torch.empty(T, w, dtype=torch.bfloat16, device=x.device) if fast else None
+        kernels.conv_rows(u, proj, off["x"], self.x_bias, self.conv_w, self.conv_b, view.state, batch, u16=u16)
         decay = torch.empty(T, w, dtype=f32, device=x.device)
         inp = torch.empty(T, w, dtype=f32, device=x.device)
-        kernels.gate_rows(decay, inp, u, self.w_a, self.w_i, self.a_bias, self.i_bias, self.rate)
+        if fast:
+            kernels.gate_rows_tc(decay, inp, u, u16, self.w_a, self.w_i, self.a_bias, self.i_bias, self.rate)
+        else:
+            kernels.gate_rows(decay, inp, u, self.w_a, self.w_i, self.a_bias, self.i_bias, self.rate)
         y = torch.empty(T, w, dtype=x.dtype, device=x.device)
         kernels.decay_scan(y, decay, inp, proj, off["y"], off["x"], self.y_bias, self.x_bias, view.state, batch)
         return linear_split(y, self.w_o, wide=self.wide)

@@ -81,7 +81,7 @@ def recurrent_weights(width, blocks, taps, seed):
             "lam": torch.linspace(-7.0, 1.5, width, dtype=F64)}      # decays from a = 0.99 a token down to nothing
 
 
-@pytest.mark.parametrize("width,blocks,taps", [(44, 1, 1), (30, 3, 4), (256, 2, 4), (26, 13, 5), (128, 8, 2), (300, 4, 3)])
+@pytest.mark.parametrize("width,blocks,taps", [(44, 1, 1), (30, 3, 4), (256, 2, 4), (26, 13, 5), (128, 8, 2), (300, 4, 3), (640, 2, 3)])
 def test_convolution_gates_and_scan(K, width, blocks, taps):
     w = recurrent_weights(width, blocks, taps, width)
     lens, slots = [23, 1, 6, 2], [4, 0, 2, 5]
@@ -326,4 +326,27 @@ def test_expert_products_on_the_tensor_cores(K, E, top, H, F, T, limit, tiles):
     sout = torch.empty(1, T, H, device=DEV)
     K.expert_rows_tc(sout, smid, sd, n_tokens=T, top=1)
     close(sout[0], plain.sigmoid(h @ W["m.shared.sg"].T) * plain.clamped_expert(h, W, "m.shared.", 0.9), 2e-2)
+    K.check_device_errors(DEV)
+
+
+@pytest.mark.parametrize("width,blocks,T", [(128, 8, 70), (256, 2, 300), (144, 3, 64), (1024, 4, 700), (320, 1, 129)])
+def test_gates_on_the_tensor_cores(K, width, blocks, T):
+    """The block-diagonal products of the gates as a grouped tensor-core product (blocks of 16 to 320 channels:
+    K below, at and beyond a K step of 64, output tiles that end inside 128; rows in one to three tiles), against the
+    plain functions on the bfloat16 rounding of u that the products read."""
+    w = recurrent_weights(width, blocks, 2, width + T)
+    w["wa"], w["wi"] = w["wa"].bfloat16().double(), w["wi"].bfloat16().double()
+    u = torch.randn(T, width, generator=torch.Generator().manual_seed(T), dtype=F64).float()
+    u16 = u.bfloat16()
+    bw = width // blocks
+    ub = u16.double().view(T, blocks, bw)
+    r = plain.sigmoid(torch.einsum("boi,tbi->tbo", w["wa"], ub) + w["ba"].view(blocks, -1)).reshape(T, width)
+    i = plain.sigmoid(torch.einsum("boi,tbi->tbo", w["wi"], ub) + w["bi"].view(blocks, -1)).reshape(T, width)
+    a = torch.exp(-8.0 * r * plain.softplus(w["lam"]))
+    dev = lambda t, dt=torch.float32: t.to(dt).to(DEV).contiguous()
+    decay, inp = torch.empty(T, width, device=DEV), torch.empty(T, width, device=DEV)
+    K.gate_rows_tc(decay, inp, dev(u), dev(u16, torch.bfloat16), dev(w["wa"], torch.bfloat16), dev(w["wi"], torch.bfloat16),
+                   dev(w["ba"]), dev(w["bi"]), dev(8.0 * plain.softplus(w["lam"])))
+    close(decay, 1.0 - a, 1e-5)
+    close(inp, torch.sqrt(1.0 - a * a) * i * u.double(), 1e-5)
     K.check_device_errors(DEV)
