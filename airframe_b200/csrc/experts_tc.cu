@@ -252,12 +252,12 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_c
 #pragma unroll
             for (int j = 0; j < CW; ++j) {
               if (j >= n) continue;
-              const float r = 1.f / (1.f + expf(-(g[j] + ab)));
-              const float i = 1.f / (1.f + expf(-(u[j] + ib)));
-              const float la = -rt * r;                               // log a
+              const float r = __fdividef(1.f, 1.f + expf(-(g[j] + ab)));
+              const float i = __fdividef(1.f, 1.f + expf(-(u[j] + ib)));
+              const float d = -expm1f(-rt * r);                       // 1 - a, a = exp(-rate r)
               const size_t at = (size_t)(row0 + c0 + j) * ldu + col;
-              static_cast<float*>(a.out)[at] = -expm1f(la);           // 1 - a
-              a.out2[at] = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * i * uv[j];
+              static_cast<float*>(a.out)[at] = d;
+              a.out2[at] = sqrtf(d * (2.f - d)) * i * uv[j];          // 1 - a^2 = (1 - a)(1 + a)
             }
           }
           continue;
@@ -267,14 +267,13 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_c
         int pair = -1;
         if (lane < CW && r < rows) pair = a.perm != nullptr ? __ldcg(a.perm + row0 + r) : row0 + r;
         float s_l = 1.f, post_l = 1.f;
-        long long dst_l = -1;
+        int dst_l = -1;                                   // (DOWN: the row of out, top * n_tokens of them)
         if (pair >= 0) {
           if constexpr (DUAL) {
             if (a.pair_weight != nullptr) s_l = __ldcg(a.pair_weight + pair);
             if (a.scale_out != nullptr) post_l = __ldcg(a.scale_out + pair / a.top);
-            dst_l = row0 + r;
           } else {
-            dst_l = (long long)(pair % a.top) * a.n_tokens + pair / a.top;
+            dst_l = (pair % a.top) * a.n_tokens + pair / a.top;
           }
         }
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -284,16 +283,22 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_c
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty);
         }
+        const int n = min(CW, rows - c0);                 // (sorted rows: the chunk's first n are the tile's)
+        if constexpr (DUAL) {
+          const bool scaled = a.pair_weight != nullptr, posted = a.scale_out != nullptr;
+          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.out) + (size_t)(row0 + c0) * a.N + f;
 #pragma unroll
-        for (int j = 0; j < CW; ++j) {
-          const long long dst = __shfl_sync(0xffffffffu, dst_l, j);
-          const float s = __shfl_sync(0xffffffffu, s_l, j);
-          const float post = __shfl_sync(0xffffffffu, post_l, j);
-          if (dst < 0 || f >= a.N) continue;
-          if constexpr (DUAL) {
-            static_cast<__nv_bfloat16*>(a.out)[(size_t)dst * a.N + f] =
-                __float2bfloat16_rn(ex_act(s * g[j], s * u[j], a.limit) * post);
-          } else {
+          for (int j = 0; j < CW; ++j) {
+            const float s = scaled ? __shfl_sync(0xffffffffu, s_l, j) : 1.f;
+            const float post = posted ? __shfl_sync(0xffffffffu, post_l, j) : 1.f;
+            if (j >= n || f >= a.N) continue;
+            o[(size_t)j * a.N] = __float2bfloat16_rn(ex_act(s * g[j], s * u[j], a.limit) * post);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < CW; ++j) {
+            const int dst = __shfl_sync(0xffffffffu, dst_l, j);
+            if (dst < 0 || f >= a.N) continue;
             static_cast<float*>(a.out)[(size_t)dst * a.N + f] = g[j];
           }
         }
@@ -390,7 +395,8 @@ AF_EXPORT int af_gate_rows_tc(float* decay, float* input, const float* u, const 
   AF_REQUIRE(n_rows > 0 && blocks > 0 && bw > 0 && bw % 8 == 0, "af_gate_rows_tc: %d blocks of %d channels", blocks, bw);
   AF_REQUIRE(((uintptr_t)u16 & 15) == 0 && ((uintptr_t)wa & 15) == 0 && ((uintptr_t)wi & 15) == 0,
              "af_gate_rows_tc: operands must be 16-byte aligned");
-  const int tile = n_rows <= 16 ? 16 : n_rows <= 32 ? 32 : n_rows <= 64 ? 64 : n_rows <= 128 ? 128 : 256;
+  // (the products are short and the epilogue is long: small row tiles, a block each, two blocks an SM)
+  const int tile = n_rows <= 16 ? 16 : n_rows <= 32 ? 32 : 64;
   const long long width = (long long)blocks * bw;
   CUtensorMap m0, m1, mx;
   int rc = af_make_map_bf16(&m0, wa, width, bw, bw, EX_BM);
