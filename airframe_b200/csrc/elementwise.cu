@@ -762,7 +762,8 @@ AF_EXPORT int af_add_normed_terms(float* x, const void* a, int a_dtype, int a_pa
   const size_t part_stride = (size_t)n_rows * hidden;
   if (hidden % 4 == 0 && hidden <= 8192 &&
       (((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w_post | (uintptr_t)w_next | (uintptr_t)y) & 15) == 0) {
-    const int nv = hidden > 4096 ? 2 : 1;
+    // (many rows: two groups a thread, so that more rows share an SM and their phases overlap)
+    const int nv = (n_rows >= 256 && hidden >= 1024) || hidden > 4096 ? 2 : 1;
     const int row_threads = ((hidden / (4 * nv) + 31) / 32) * 32;
     if (nv == 2) {
       AF_DISPATCH_DTYPE(y_dtype, TY,

@@ -235,7 +235,7 @@ __device__ __forceinline__ float gelu_tanh_f32(float z) {
 // in a row and composes their maps S -> S - d S + b (d = 1 - a; two such maps compose to d = d1 + d2 - d1 d2),
 // the warps exchange the pairs, each warp composes the pairs of the
 // warps before it onto the state carried so far and then walks its tokens from the state that really enters them.
-#define AF_DS_WARPS 8
+#define AF_DS_WARPS 16      // at most; a step of single tokens runs with one
 #define AF_DS_RUN 16
 template <typename TY>
 __global__ void __launch_bounds__(AF_DS_WARPS * 32)
@@ -245,7 +245,7 @@ decay_scan_kernel(TY* __restrict__ out, const float* __restrict__ decay, const f
                   const int* __restrict__ slots, int width, int taps) {
   pdl_launch_dependents();
   __shared__ float comp[AF_DS_WARPS][32][2];
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int c = blockIdx.x * 32 + lane;
   const int b = blockIdx.y;
   const bool on = c < width;
@@ -258,12 +258,12 @@ decay_scan_kernel(TY* __restrict__ out, const float* __restrict__ decay, const f
   proj = pdl_fresh(proj);
   if (slot < 0) {
     if (on)
-      for (int t = first + w; t < last; t += AF_DS_WARPS) out[(size_t)t * width + c] = from_f32<TY>(0.f);
+      for (int t = first + w; t < last; t += nw) out[(size_t)t * width + c] = from_f32<TY>(0.f);
     return;
   }
   float* srow = state + (size_t)slot * taps * width;
   float carry = on ? srow[c] : 0.f;
-  for (int base = first; base < last; base += AF_DS_WARPS * AF_DS_RUN) {
+  for (int base = first; base < last; base += nw * AF_DS_RUN) {
     const int t0 = base + w * AF_DS_RUN;
     const int n = max(0, min(AF_DS_RUN, last - t0));
     float a[AF_DS_RUN], v[AF_DS_RUN], g[AF_DS_RUN];
@@ -287,7 +287,7 @@ decay_scan_kernel(TY* __restrict__ out, const float* __restrict__ decay, const f
     comp[w][lane][1] = B;
     __syncthreads();
     float S = carry, full = carry;
-    for (int x = 0; x < AF_DS_WARPS; ++x) {
+    for (int x = 0; x < nw; ++x) {
       if (x == w) S = full;
       full = fmaf(-comp[x][lane][0], full, full) + comp[x][lane][1];
     }
@@ -317,12 +317,17 @@ decay_scan_kernel(TY* __restrict__ out, const float* __restrict__ decay, const f
 
 AF_EXPORT int af_decay_scan(void* out, int out_dtype, const float* decay, const float* input, const float* proj,
                             long long ld, int off_y, int off_x, const float* by, const float* bx, float* state,
-                            const int* seq_starts, const int* slots, int n_seqs, int width, int taps,
+                            const int* seq_starts, const int* slots, int n_seqs, int n_tokens, int width, int taps,
                             cudaStream_t stream) {
   if (n_seqs == 0) return 0;
-  AF_REQUIRE(n_seqs > 0 && n_seqs < 65536 && width > 0 && taps >= 1, "af_decay_scan: bad sizes");
+  AF_REQUIRE(n_seqs > 0 && n_seqs < 65536 && n_tokens >= 0 && width > 0 && taps >= 1, "af_decay_scan: bad sizes");
+  // warps by the tokens a sequence is likely to have in this step (any number is correct): one for single tokens,
+  // up to AF_DS_WARPS for a prompt
+  const int most = n_tokens - (n_seqs - 1);
+  int warps = 1;
+  while (warps < AF_DS_WARPS && warps * AF_DS_RUN < most) warps *= 2;
   AF_DISPATCH_DTYPE(out_dtype, TY,
-                    af_launch(decay_scan_kernel<TY>, dim3((width + 31) / 32, n_seqs), dim3(AF_DS_WARPS * 32), 0, stream,
+                    af_launch(decay_scan_kernel<TY>, dim3((width + 31) / 32, n_seqs), dim3(warps * 32), 0, stream,
                               (TY*)out, decay, input, proj, ld, off_y, off_x, by, bx, state, seq_starts, slots, width,
                               taps));
   AF_CHECK_LAUNCH("af_decay_scan");

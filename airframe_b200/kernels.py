@@ -1292,8 +1292,8 @@ def decay_scan(out, decay, inp, proj, off_y: int, off_x: int, by, bx, state, bat
     _check(_lib().af_decay_scan(_ptr(out), c_int(dtype_code(out.dtype)), _ptr(decay), _ptr(inp), pp, ld, c_int(off_y),
                                 c_int(off_x), _ptr(by, "by", torch.float32), _ptr(bx, "bx", torch.float32),
                                 _ptr(state, "state", torch.float32), _ptr(batch.seq_starts, "seq_starts", torch.int32),
-                                _ptr(batch.slots, "slots", torch.int32), c_int(batch.n_seqs), c_int(width), c_int(taps),
-                                _stream()))
+                                _ptr(batch.slots, "slots", torch.int32), c_int(batch.n_seqs), c_int(out.shape[0]), c_int(width),
+                                c_int(taps), _stream()))
 
 
 # ---------------------------------------------------------------- routed experts

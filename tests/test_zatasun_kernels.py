@@ -250,9 +250,9 @@ def test_whole_norm_and_rotation(K, nq, nkv, hd, dv, rot, scaling, dtype):
 
 # ---------------------------------------------------------------- x += norm(a weighted sum)
 
-@pytest.mark.parametrize("H", [50, 72, 256])
+@pytest.mark.parametrize("H", [50, 72, 256, 1032, 4104])
 def test_residual_step_norms_a_weighted_sum(K, H):
-    T = 21
+    T = 300 if H == 1032 else 21        # (many rows of some width: two groups of four values a thread)
     g = torch.Generator().manual_seed(H)
     x = torch.randn(T, H, generator=g)
     a, b, parts = torch.randn(T, H, generator=g), torch.randn(T, H, generator=g).bfloat16(), torch.randn(3, T, H, generator=g)
