@@ -824,6 +824,100 @@ qk_whole_norm_rope_store_kernel(T* __restrict__ qkv, long long out_stride, const
   }
 }
 
+// The same with the token's projection row in shared memory (rows of up to 12,288 values, the norm in front of the
+// rotation, values of their own): the row is read once, both mean squares leave one reduction, the cache row is
+// looked up once a token, and the pairs of all heads are one flat loop whose loads do not wait for one another.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_whole_norm_rope_row_kernel(T* __restrict__ qkv, long long out_stride, const float* __restrict__ proj, long long ld,
+                              const float* __restrict__ bias, const float* __restrict__ q_weight,
+                              const float* __restrict__ k_weight, float eps, float magnitude,
+                              const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                              const int* __restrict__ slots, const int* __restrict__ len_after,
+                              const float* __restrict__ inv_freq, const float2* __restrict__ table, int nq, int nkv,
+                              int hd, int dv, int rot_dim, int pairing, T* __restrict__ kcache, T* __restrict__ vcache,
+                              const int* __restrict__ page_table, int max_pages, int ring_rows, int pitch) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) float srow[];          // q | k | v of the token, biases added
+  __shared__ float red[2][8];
+  __shared__ T* cache_rows[2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int pk = pitch > 0 ? pitch : hd, pv = pitch > 0 ? pitch : dv;
+  if (threadIdx.x == 0) {                                // (the step's tables are there before the step begins)
+    T *k0 = nullptr, *v0 = nullptr;
+    qk_cache_rows(kcache, vcache, seq_of_token, slots, len_after, page_table, max_pages, ring_rows, nkv, t, pos, 0, pk,
+                  pv, &k0, &v0);
+    cache_rows[0] = k0, cache_rows[1] = v0;
+  }
+  pdl_wait();
+  const float* row = proj + (size_t)t * ld;
+  const int n_q = nq * hd, n_k = nkv * hd, n_all = n_q + n_k + nkv * dv;
+  float sq = 0.f, sk = 0.f;
+#pragma unroll 4
+  for (int i = threadIdx.x; i < n_all; i += 256) {
+    const float v = row[i] + (bias ? bias[i] : 0.f);
+    srow[i] = v;
+    if (i < n_q) sq += v * v; else if (i < n_q + n_k) sk += v * v;
+  }
+  sq = warp_sum(sq), sk = warp_sum(sk);
+  if (lane == 0) red[0][warp] = sq, red[1][warp] = sk;
+  __syncthreads();
+  sq = sk = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) sq += red[0][w], sk += red[1][w];
+  const float inv_q = rsqrtf(sq / (float)n_q + eps), inv_k = rsqrtf(sk / (float)n_k + eps);
+  T* orow = qkv + (size_t)t * out_stride;
+  T* kd0 = cache_rows[0];
+  T* vd0 = cache_rows[1];
+  const int heads = nq + nkv, half = rot_dim / 2;
+  // (q weights and k weights: heads x hd values each, in the heads' order)
+  for (int idx = threadIdx.x; idx < heads * half; idx += 256) {
+    const int head = idx / half, p = idx % half;
+    const bool is_k = head >= nq;
+    const int i0 = pairing == AF_PAIR_HALF ? p : 2 * p, i1 = pairing == AF_PAIR_HALF ? p + half : 2 * p + 1;
+    const float* w = is_k ? k_weight + (size_t)(head - nq) * hd : q_weight + (size_t)head * hd;
+    const float inv = is_k ? inv_k : inv_q;
+    const float a = srow[head * hd + i0] * inv * w[i0], b = srow[head * hd + i1] * inv * w[i1];
+    float s, c;
+    if (table != nullptr) {
+      const float2 cs = table[(size_t)t * half + p];
+      c = cs.x, s = cs.y;
+    } else {
+      sincosf((float)pos * inv_freq[p], &s, &c);
+    }
+    s *= magnitude, c *= magnitude;
+    const T ra = from_f32<T>(a * c - b * s), rb = from_f32<T>(b * c + a * s);
+    T* dst = orow + (size_t)head * pk;
+    dst[i0] = ra, dst[i1] = rb;
+    if (is_k && kd0 != nullptr) {
+      T* kdst = kd0 + (size_t)(head - nq) * AF_PAGE * pk;
+      kdst[i0] = ra, kdst[i1] = rb;
+    }
+  }
+  const int rest = pk - rot_dim;                         // behind the rotated part: kept elements, then padding
+  for (int idx = threadIdx.x; idx < heads * rest; idx += 256) {
+    const int head = idx / rest, i = rot_dim + idx % rest;
+    const bool is_k = head >= nq;
+    float v = 0.f;
+    if (i < hd) {
+      const float* w = is_k ? k_weight + (size_t)(head - nq) * hd : q_weight + (size_t)head * hd;
+      v = srow[head * hd + i] * (is_k ? inv_k : inv_q) * w[i];
+    }
+    const T r = from_f32<T>(v);
+    orow[(size_t)head * pk + i] = r;
+    if (is_k && kd0 != nullptr) kd0[(size_t)(head - nq) * AF_PAGE * pk + i] = r;
+  }
+  T* vrow = orow + (size_t)heads * pk;
+  for (int idx = threadIdx.x; idx < nkv * pv; idx += 256) {
+    const int g = idx / pv, i = idx % pv;
+    const T r = from_f32<T>(i < dv ? srow[n_q + n_k + g * dv + i] : 0.f);
+    vrow[(size_t)g * pv + i] = r;
+    if (vd0 != nullptr) vd0[(size_t)g * AF_PAGE * pv + i] = r;
+  }
+}
+
 AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, const float* proj, long long ld,
                                     const float* bias, const float* q_weight, const float* k_weight, float eps,
                                     int norm_after, float magnitude, int v_from_k,
@@ -846,6 +940,15 @@ AF_EXPORT int af_qk_norm_rope_store(void* qkv, int dtype, long long out_stride, 
   AF_REQUIRE(ring_rows % AF_PAGE == 0, "af_qk_norm_rope_store: ring rows %d not whole pages", ring_rows);
   AF_REQUIRE((kcache == nullptr) == (vcache == nullptr), "af_qk_norm_rope_store: k and v cache");
   AF_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "af_qk_norm_rope_store: both norm weights or none");
+  const size_t row_bytes = ((size_t)(nq + nkv) * hd + (size_t)nkv * dv) * sizeof(float);
+  if (whole_norm && !norm_after && !v_from_k && row_bytes <= 48 * 1024) {
+    AF_DISPATCH_DTYPE(dtype, T,
+                      af_launch(qk_whole_norm_rope_row_kernel<T>, dim3((unsigned)n_tokens), dim3(256), row_bytes, stream,
+                                (T*)qkv, out_stride, proj, ld, bias, q_weight, k_weight, eps, magnitude, positions,
+                                seq_of_token, slots, len_after, inv_freq, tab, nq, nkv, hd, dv, rot_dim, pairing,
+                                (T*)kcache, (T*)vcache, page_table, max_pages, ring_rows, pitch));
+    AF_CHECK_LAUNCH("af_qk_norm_rope_store");
+  }
   if (whole_norm) {
     AF_DISPATCH_DTYPE(dtype, T,
                       af_launch(qk_whole_norm_rope_store_kernel<T>, dim3((unsigned)n_tokens), dim3(256), 0, stream, (T*)qkv,
