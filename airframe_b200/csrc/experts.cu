@@ -30,47 +30,77 @@ __device__ __forceinline__ void load4_f32<__nv_bfloat16>(float* v, const __nv_bf
   v[2] = __uint_as_float(raw.y << 16), v[3] = __uint_as_float(raw.y & 0xffff0000u);
 }
 
-// One block per token; a warp per expert at a time.  Few tokens (a decode step) get a warp for every expert.
-template <typename TX>
-__global__ void __launch_bounds__(1024)
-expert_route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ shared_gate,
-                    const TX* __restrict__ h, const float* __restrict__ router, int hidden, int n_experts, int top) {
+// Scores first, the choice behind them.  A warp of the scores' kernel takes one row of the router (an expert, or
+// the shared expert's gate) and TM tokens, and adds a token's products in one fixed order whatever TM is, so that a
+// prompt and a decode step choose alike; the warps of a block share their tokens.  scores: [tokens, rows].
+template <typename TX, int TM>
+__global__ void __launch_bounds__(256)
+expert_score_kernel(float* __restrict__ scores, const TX* __restrict__ h, const float* __restrict__ router, int n_tokens,
+                    int hidden, int rows) {
   pdl_launch_dependents();
-  extern __shared__ float score[];                  // n_experts (+ 1) scores
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-  const int t = blockIdx.x;
-  const int rows = n_experts + (shared_gate != nullptr ? 1 : 0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long job = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+  const long long groups = (n_tokens + TM - 1) / TM;
+  if (job >= groups * rows) return;
+  const int t0 = (int)(job / rows) * TM, e = (int)(job % rows);
+  const float* w = router + (size_t)e * hidden;
+  const bool vec = hidden % 4 == 0 && (((uintptr_t)h | (uintptr_t)router) & 15) == 0;
   pdl_wait();
   h = pdl_fresh(h);
-  const TX* x = h + (size_t)t * hidden;
-  const bool vec = hidden % 4 == 0 && (((uintptr_t)h | (uintptr_t)router) & 15) == 0;
-  for (int e = warp; e < rows; e += nwarp) {
-    const float* w = router + (size_t)e * hidden;
-    float z = 0.f;
-    if (vec) {                                      // four values a lane and load, four loads in flight
-      float zz[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int i0 = lane * 4; i0 < hidden; i0 += 512) {
+  float z[TM];
+  if (vec) {                                        // four values a lane and load, four loads in flight
+    float zz[TM][4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + u * 128;
-          if (i < hidden) {
-            const float4 wv = *reinterpret_cast<const float4*>(w + i);
+    for (int m = 0; m < TM; ++m) zz[m][0] = zz[m][1] = zz[m][2] = zz[m][3] = 0.f;
+    for (int i0 = lane * 4; i0 < hidden; i0 += 512) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * 128;
+        if (i < hidden) {
+          const float4 wv = *reinterpret_cast<const float4*>(w + i);
+#pragma unroll
+          for (int m = 0; m < TM; ++m) {
+            if (t0 + m >= n_tokens) continue;
             float xv[4];
-            load4_f32<TX>(xv, x + i);
-            zz[u] = fmaf(wv.x, xv[0], fmaf(wv.y, xv[1], fmaf(wv.z, xv[2], fmaf(wv.w, xv[3], zz[u]))));
+            load4_f32<TX>(xv, h + (size_t)(t0 + m) * hidden + i);
+            zz[m][u] = fmaf(wv.x, xv[0], fmaf(wv.y, xv[1], fmaf(wv.z, xv[2], fmaf(wv.w, xv[3], zz[m][u]))));
           }
         }
       }
-      z = (zz[0] + zz[1]) + (zz[2] + zz[3]);
-    } else {
-      for (int i = lane; i < hidden; i += 32) z = fmaf(w[i], to_f32<TX>(x[i]), z);
     }
-    z = warp_sum(z);
-    if (lane == 0) score[e] = 1.f / (1.f + expf(-z));
+#pragma unroll
+    for (int m = 0; m < TM; ++m) z[m] = (zz[m][0] + zz[m][1]) + (zz[m][2] + zz[m][3]);
+  } else {
+#pragma unroll
+    for (int m = 0; m < TM; ++m) {
+      z[m] = 0.f;
+      if (t0 + m >= n_tokens) continue;
+      const TX* x = h + (size_t)(t0 + m) * hidden;
+      for (int i = lane; i < hidden; i += 32) z[m] = fmaf(w[i], to_f32<TX>(x[i]), z[m]);
+    }
   }
-  __syncthreads();
-  if (warp != 0) return;
-  if (shared_gate != nullptr && lane == 0) shared_gate[t] = score[n_experts];
+#pragma unroll
+  for (int m = 0; m < TM; ++m) {
+    const float zs = warp_sum(z[m]);
+    if (lane == 0 && t0 + m < n_tokens) scores[(size_t)(t0 + m) * rows + e] = 1.f / (1.f + expf(-zs));
+  }
+}
+
+// A warp a token: the `top` largest scores in turn (equal scores: the lower index), each struck out once chosen.
+__global__ void __launch_bounds__(128)
+expert_choose_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ shared_gate,
+                     const float* __restrict__ scores, int n_tokens, int n_experts, int rows, int top) {
+  pdl_launch_dependents();
+  extern __shared__ float score_all[];              // a row of n_experts scores a warp
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  pdl_wait();
+  if (t >= n_tokens) return;
+  scores = pdl_fresh(scores);
+  float* score = score_all + (size_t)warp * n_experts;
+  for (int e = lane; e < n_experts; e += 32) score[e] = scores[(size_t)t * rows + e];
+  if (shared_gate != nullptr && lane == 0) shared_gate[t] = scores[(size_t)t * rows + n_experts];
+  __syncwarp();
   for (int k = 0; k < top; ++k) {
     float best = -1.f;                              // (a sigmoid is never negative; a chosen expert's score is set to -2)
     int at = n_experts;
@@ -91,18 +121,34 @@ expert_route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __res
   }
 }
 
-AF_EXPORT int af_expert_route(int* ids, float* wts, float* shared_gate, const void* h, int h_dtype, const float* router,
-                              int n_tokens, int hidden, int n_experts, int top, cudaStream_t stream) {
+// scores: room for n_tokens x (n_experts + 1) floats.
+AF_EXPORT int af_expert_route(int* ids, float* wts, float* shared_gate, float* scores, const void* h, int h_dtype,
+                              const float* router, int n_tokens, int hidden, int n_experts, int top,
+                              cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  AF_REQUIRE(n_tokens > 0 && hidden > 0 && n_experts > 0 && top >= 1 && top <= n_experts,
+  AF_REQUIRE(n_tokens > 0 && hidden > 0 && n_experts > 0 && top >= 1 && top <= n_experts && scores != nullptr,
              "af_expert_route: %d of %d experts", top, n_experts);
   AF_REQUIRE(n_experts <= 8192, "af_expert_route: up to 8192 experts");
-  const size_t smem = (size_t)(n_experts + 1) * sizeof(float);
   const int rows = n_experts + (shared_gate != nullptr ? 1 : 0);
-  const int threads = n_tokens > 1024 ? 128 : (rows >= 32 ? 1024 : rows <= 4 ? 128 : 32 * rows);
-  AF_DISPATCH_DTYPE(h_dtype, TX,
-                    af_launch(expert_route_kernel<TX>, dim3(n_tokens), dim3(threads), smem, stream, ids, wts, shared_gate,
-                              (const TX*)h, router, hidden, n_experts, top));
+  // a prompt: four tokens a warp (a row of the router is read once for them); few tokens: a warp each
+  const int tm = n_tokens >= 256 ? 4 : 1;
+  const long long jobs = (long long)((n_tokens + tm - 1) / tm) * rows;
+  const long long blocks = (jobs + 7) / 8;
+  AF_REQUIRE(blocks < (1ll << 31), "af_expert_route: too many tokens");
+  if (tm == 4) {
+    AF_DISPATCH_DTYPE(h_dtype, TX,
+                      af_launch(expert_score_kernel<TX, 4>, dim3((unsigned)blocks), dim3(256), 0, stream, scores,
+                                (const TX*)h, router, n_tokens, hidden, rows));
+  } else {
+    AF_DISPATCH_DTYPE(h_dtype, TX,
+                      af_launch(expert_score_kernel<TX, 1>, dim3((unsigned)blocks), dim3(256), 0, stream, scores,
+                                (const TX*)h, router, n_tokens, hidden, rows));
+  }
+  AF_COUNT_LAUNCH("af_expert_route");
+  const int warps = n_experts <= 2048 ? 4 : 1;
+  af_launch(expert_choose_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps),
+            (size_t)warps * n_experts * sizeof(float), stream, ids, wts, shared_gate, (const float*)scores, n_tokens,
+            n_experts, rows, top);
   AF_CHECK_LAUNCH("af_expert_route");
 }
 

@@ -1326,8 +1326,9 @@ def expert_route(ids, wts, shared_gate, h, router, n_experts: int) -> None:
     if tuple(ids.shape) != (T, top) or tuple(wts.shape) != (T, top) or not (ids.is_contiguous() and wts.is_contiguous()
                                                                            and h.is_contiguous()):
         raise KernelError("expert_route: ids and wts contiguous [T, top], h contiguous")
+    scores = torch.empty(T, rows, dtype=torch.float32, device=h.device)      # (between the two kernels)
     _check(_lib().af_expert_route(_ptr(ids, "ids", torch.int32), _ptr(wts, "wts", torch.float32),
-                                  _ptr(shared_gate, "shared_gate", torch.float32, allow_none=True), _ptr(h),
+                                  _ptr(shared_gate, "shared_gate", torch.float32, allow_none=True), _ptr(scores), _ptr(h),
                                   c_int(dtype_code(h.dtype)), _ptr(router), c_int(T), c_int(H), c_int(n_experts),
                                   c_int(top), _stream()))
 

@@ -146,8 +146,9 @@ class RoutedExperts(FeedForward):
         return 4 if self.ctx.compute_dtype == torch.float32 else 2
 
     def decode_bytes(self, lens) -> int:
-        used = min(self.n_experts, len(lens) * self.top)        # at most so many experts' matrices are read
-        total = 3 * used * self.hidden * self.inter * self._el() + 4 * self.router.numel()
+        # the experts whose matrices are read: the expected number under a router that chooses evenly
+        used = self.n_experts * (1.0 - (1.0 - self.top / self.n_experts) ** len(lens))
+        total = int(3 * used * self.hidden * self.inter * self._el()) + 4 * self.router.numel()
         if self.shared is not None:
             total += 3 * self.hidden * int(self.shared["intermediate_size"]) * self._el()
         return total

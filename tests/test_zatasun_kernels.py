@@ -210,6 +210,30 @@ def test_router_plan_and_expert_products(K, E, top, H, F, T, limit, dtype):
     close(out.sum(0), want, 2e-5 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("E,top,H", [(5, 2, 72), (7, 3, 50), (40, 4, 256)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_router_chooses_alike_for_a_prompt_and_for_single_tokens(K, E, top, H, dtype):
+    """The router over a prompt of 1,030 tokens (several tokens a block) against the plain scores, and bit for bit
+    against the same tokens routed a few at a time (the form a decode step takes)."""
+    T = 1030
+    g = torch.Generator().manual_seed(E)
+    h = torch.randn(T, H, generator=g).bfloat16().double()
+    router = torch.randn(E + 1, H, generator=g, dtype=F64) / math.sqrt(H)
+    x, r = h.to(dtype).to(DEV), router.float().to(DEV)
+    ids, wts, mix = torch.empty(T, top, dtype=torch.int32, device=DEV), torch.empty(T, top, device=DEV), torch.empty(T, device=DEV)
+    K.expert_route(ids, wts, mix, x, r, E)
+    s = plain.sigmoid(h @ router[:E].float().double().T)
+    best = s.sort(dim=1, descending=True).values[:, :top]
+    close(wts, best, 2e-6)
+    close(mix, plain.sigmoid(h @ router[E:].float().double().T)[:, 0], 2e-6)
+    for first in (0, 512, 1027):
+        n = min(3, T - first)
+        ids1, wts1, mix1 = torch.empty(n, top, dtype=torch.int32, device=DEV), torch.empty(n, top, device=DEV), torch.empty(n, device=DEV)
+        K.expert_route(ids1, wts1, mix1, x[first:first + n].contiguous(), r, E)
+        assert torch.equal(ids1, ids[first:first + n]) and torch.equal(wts1, wts[first:first + n])
+        assert torch.equal(mix1, mix[first:first + n])
+
+
 # ---------------------------------------------------------------- the norm over a whole projection, and the rotation
 
 @pytest.mark.parametrize("nq,nkv,hd,dv,rot,scaling", [(4, 4, 12, 20, 6, None), (2, 1, 20, 20, 20, (8.0, 1.0, 3.0, 64)),
