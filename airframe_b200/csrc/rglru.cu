@@ -22,9 +22,10 @@ conv_rows_kernel(float* __restrict__ u, __nv_bfloat16* __restrict__ u16, const f
                  const float* __restrict__ state, const int* __restrict__ seq_of_token,
                  const int* __restrict__ seq_starts, const int* __restrict__ slots, int n_tokens, int width, int taps) {
   pdl_launch_dependents();
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)n_tokens * width) return;
-  const int t = (int)(i / width), c = (int)(i % width);
+  // (a block: 256 channels of one token; no division a value)
+  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  const size_t i = (size_t)t * width + c;
   const int seq = seq_of_token[t];
   const int first = seq_starts[seq];
   const int slot = slots[seq];
@@ -42,10 +43,65 @@ conv_rows_kernel(float* __restrict__ u, __nv_bfloat16* __restrict__ u16, const f
       // before the step: row 1 + (taps - 1) + (src - first) of the state (zeros for a sequence that just began)
       v = slot >= 0 ? state[((size_t)slot * taps + (taps + src - first)) * width + c] : 0.f;
     }
-    acc += cw[(size_t)c * taps + k] * v;
+    acc += cw[(size_t)k * width + c] * v;           // (taps stored [taps, width]: a warp reads one line)
   }
   u[i] = acc;
   if (u16 != nullptr) u16[i] = __float2bfloat16_rn(acc);      // (what a tensor-core product of the gates reads)
+}
+
+// Up to eight taps: a thread takes one channel of four consecutive tokens.  The inputs of its window are asked for
+// before it knows where the tokens' sequences begin (the tables' loads and the window's run side by side, and a
+// value is read once for the four tokens); a tap that reaches before a sequence's first token of the step takes
+// the slot's history instead.  Every output adds its taps from the oldest to the newest.
+#define AF_CV_TOKENS 4
+#define AF_CV_TAPS 8
+__global__ void __launch_bounds__(256)
+conv_rows_window_kernel(float* __restrict__ u, __nv_bfloat16* __restrict__ u16, const float* __restrict__ proj,
+                        long long ld, int off_x, const float* __restrict__ bx, const float* __restrict__ cw,
+                        const float* __restrict__ cb, const float* __restrict__ state,
+                        const int* __restrict__ seq_of_token, const int* __restrict__ seq_starts,
+                        const int* __restrict__ slots, int n_tokens, int width, int taps) {
+  pdl_launch_dependents();
+  const int t0 = blockIdx.x * AF_CV_TOKENS, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  int first[AF_CV_TOKENS], slot[AF_CV_TOKENS];
+#pragma unroll
+  for (int e = 0; e < AF_CV_TOKENS; ++e) {
+    const int seq = t0 + e < n_tokens ? seq_of_token[t0 + e] : -1;
+    first[e] = seq >= 0 ? seq_starts[seq] : 0;
+    slot[e] = seq >= 0 ? slots[seq] : -1;
+  }
+  const float xb = bx[c], bias = cb[c];
+  float tap[AF_CV_TAPS];                              // tap[d]: the weight on the token d back
+#pragma unroll
+  for (int d = 0; d < AF_CV_TAPS; ++d) tap[d] = d < taps ? cw[(size_t)(taps - 1 - d) * width + c] : 0.f;
+  pdl_wait();
+  proj = pdl_fresh(proj);
+  state = pdl_fresh(state);
+  float win[AF_CV_TOKENS + AF_CV_TAPS - 1];           // win[j]: the input of token t0 - (AF_CV_TAPS - 1) + j
+#pragma unroll
+  for (int j = 0; j < AF_CV_TOKENS + AF_CV_TAPS - 1; ++j) {
+    const int src = t0 - (AF_CV_TAPS - 1) + j;
+    win[j] = (j >= AF_CV_TAPS - taps && src >= 0 && src < n_tokens) ? proj[(size_t)src * ld + off_x + c] + xb : 0.f;
+  }
+#pragma unroll
+  for (int e = 0; e < AF_CV_TOKENS; ++e) {
+    const int t = t0 + e;
+    if (t >= n_tokens) break;
+    float acc = bias;
+#pragma unroll
+    for (int d = AF_CV_TAPS - 1; d >= 0; --d) {
+      if (d >= taps) continue;
+      const int src = t - d;
+      float v = win[AF_CV_TAPS - 1 + e - d];
+      if (src < first[e])                             // before the step: the slot's history (zeros for a new sequence)
+        v = slot[e] >= 0 ? state[((size_t)slot[e] * taps + (taps + src - first[e])) * width + c] : 0.f;
+      acc += tap[d] * v;
+    }
+    const size_t i = (size_t)t * width + c;
+    u[i] = acc;
+    if (u16 != nullptr) u16[i] = __float2bfloat16_rn(acc);
+  }
 }
 
 AF_EXPORT int af_conv_rows(float* u, void* u16, const float* proj, long long ld, int off_x, const float* bx, const float* cw,
@@ -53,9 +109,15 @@ AF_EXPORT int af_conv_rows(float* u, void* u16, const float* proj, long long ld,
                            const int* slots, int n_tokens, int width, int taps, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   AF_REQUIRE(n_tokens > 0 && width > 0 && taps >= 1, "af_conv_rows: bad sizes");
-  const size_t blocks = ((size_t)n_tokens * width + 255) / 256;
-  AF_REQUIRE(blocks < (1ull << 31), "af_conv_rows: too many rows");
-  af_launch(conv_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, u, (__nv_bfloat16*)u16, proj, ld, off_x, bx, cw, cb, state,
+  const int chunks = (width + 255) / 256;
+  AF_REQUIRE(chunks < 65536, "af_conv_rows: too many channels");
+  if (taps <= AF_CV_TAPS) {
+    af_launch(conv_rows_window_kernel, dim3((unsigned)((n_tokens + AF_CV_TOKENS - 1) / AF_CV_TOKENS), (unsigned)chunks),
+              dim3(256), 0, stream, u, (__nv_bfloat16*)u16, proj, ld, off_x, bx, cw, cb, state, seq_of_token, seq_starts,
+              slots, n_tokens, width, taps);
+    AF_CHECK_LAUNCH("af_conv_rows");
+  }
+  af_launch(conv_rows_kernel, dim3((unsigned)n_tokens, (unsigned)chunks), dim3(256), 0, stream, u, (__nv_bfloat16*)u16, proj, ld, off_x, bx, cw, cb, state,
             seq_of_token, seq_starts, slots, n_tokens, width, taps);
   AF_CHECK_LAUNCH("af_conv_rows");
 }

@@ -1204,15 +1204,15 @@ def scale_(z, s: float) -> None:
 
 def conv_rows(u, proj, off_x: int, bx, cw, cb, state, batch, u16=None) -> None:
     """u = the causal convolution per channel of (section ``off_x`` of the float32 projection rows + bx), plus
-    cb: ``cw`` float32 [width, taps], the last tap on the current token; the tokens before the step come from
+    cb: ``cw`` float32 [taps, width] (the stored taps transposed), the last tap on the current token; the tokens before the step come from
     rows 1 .. taps-1 of the sequence's ``state`` (float32 [slots, taps, width]; zeros for a new sequence).
     ``u16`` (bfloat16, like u): also receives u, rounded."""
     T, width = u.shape
     if u16 is not None and (u16.dtype != torch.bfloat16 or u16.shape != u.shape or not u16.is_contiguous()):
         raise KernelError("conv_rows: u16 is a contiguous bfloat16 tensor of u's shape")
-    taps = cw.shape[1]
-    if u.dtype != torch.float32 or not u.is_contiguous() or tuple(cw.shape) != (width, taps) or not cw.is_contiguous():
-        raise KernelError(f"conv_rows: u contiguous float32 [T, {width}], taps [{width}, taps]")
+    taps = cw.shape[0]
+    if u.dtype != torch.float32 or not u.is_contiguous() or tuple(cw.shape) != (taps, width) or not cw.is_contiguous():
+        raise KernelError(f"conv_rows: u contiguous float32 [T, {width}], taps [taps, {width}]")
     if tuple(state.shape[1:]) != (taps, width) or state.dtype != torch.float32 or not state.is_contiguous():
         raise KernelError(f"conv_rows: state must be contiguous float32 [slots, {taps}, {width}]")
     if off_x + width > proj.shape[1] or bx.numel() != width or cb.numel() != width:

@@ -286,7 +286,7 @@ class RgLru(_StateMixer):
         self.w_in, self.off = self._pack(weights, ("y", "x"))
         self.y_bias = weights[nm["y_bias"]].to(f32).contiguous()
         self.x_bias = weights[nm["x_bias"]].to(f32).contiguous()
-        self.conv_w = weights[nm["conv"]].to(f32).contiguous()
+        self.conv_w = weights[nm["conv"]].to(f32).t().contiguous()       # [taps, width]: a warp reads a tap of 32 channels in one line
         self.conv_b = weights[nm["conv_bias"]].to(f32).contiguous()
         self.w_a = weights[nm["a"]].to(dt).contiguous()
         self.w_i = weights[nm["i"]].to(dt).contiguous()

@@ -64,7 +64,7 @@ def run_recurrent_step(K, w, proj, batch, state, out_dtype, gate_dtype):
     dev = lambda t, dt=torch.float32: t.to(dt).to(DEV).contiguous()
     rate = dev(8.0 * plain.softplus(w["lam"]))
     u = torch.empty(T, width, device=DEV)
-    K.conv_rows(u, proj, width, dev(w["bx"]), dev(w["cw"]), dev(w["cb"]), state, batch)
+    K.conv_rows(u, proj, width, dev(w["bx"]), dev(w["cw"].t()), dev(w["cb"]), state, batch)
     decay, inp = torch.empty_like(u), torch.empty_like(u)
     K.gate_rows(decay, inp, u, dev(w["wa"], gate_dtype), dev(w["wi"], gate_dtype), dev(w["ba"]), dev(w["bi"]), rate)
     y = torch.empty(T, width, dtype=out_dtype, device=DEV)
@@ -81,7 +81,7 @@ def recurrent_weights(width, blocks, taps, seed):
             "lam": torch.linspace(-7.0, 1.5, width, dtype=F64)}      # decays from a = 0.99 a token down to nothing
 
 
-@pytest.mark.parametrize("width,blocks,taps", [(44, 1, 1), (30, 3, 4), (256, 2, 4), (26, 13, 5), (128, 8, 2), (300, 4, 3), (640, 2, 3)])
+@pytest.mark.parametrize("width,blocks,taps", [(44, 1, 1), (30, 3, 4), (256, 2, 4), (26, 13, 5), (128, 8, 2), (300, 4, 3), (640, 2, 3), (48, 2, 9), (64, 4, 8)])
 def test_convolution_gates_and_scan(K, width, blocks, taps):
     w = recurrent_weights(width, blocks, taps, width)
     lens, slots = [23, 1, 6, 2], [4, 0, 2, 5]
