@@ -111,7 +111,8 @@ AF_EXPORT int af_conv_rows(float* u, void* u16, const float* proj, long long ld,
   AF_REQUIRE(n_tokens > 0 && width > 0 && taps >= 1, "af_conv_rows: bad sizes");
   const int chunks = (width + 255) / 256;
   AF_REQUIRE(chunks < 65536, "af_conv_rows: too many channels");
-  if (taps <= AF_CV_TAPS) {
+  // (a decode step's few tokens each begin in their slot's history: a value a thread serves them better)
+  if (taps <= AF_CV_TAPS && n_tokens >= 64) {
     af_launch(conv_rows_window_kernel, dim3((unsigned)((n_tokens + AF_CV_TOKENS - 1) / AF_CV_TOKENS), (unsigned)chunks),
               dim3(256), 0, stream, u, (__nv_bfloat16*)u16, proj, ld, off_x, bx, cw, cb, state, seq_of_token, seq_starts,
               slots, n_tokens, width, taps);

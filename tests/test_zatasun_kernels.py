@@ -84,7 +84,7 @@ def recurrent_weights(width, blocks, taps, seed):
 @pytest.mark.parametrize("width,blocks,taps", [(44, 1, 1), (30, 3, 4), (256, 2, 4), (26, 13, 5), (128, 8, 2), (300, 4, 3), (640, 2, 3), (48, 2, 9), (64, 4, 8)])
 def test_convolution_gates_and_scan(K, width, blocks, taps):
     w = recurrent_weights(width, blocks, taps, width)
-    lens, slots = [23, 1, 6, 2], [4, 0, 2, 5]
+    lens, slots = [61, 1, 6, 2], [4, 0, 2, 5]       # (70 rows: the convolution's window kernel, sequences that begin inside a thread's four tokens)
     g = torch.Generator().manual_seed(7)
     seqs = [torch.randn(n + 9, 2 * width, generator=g, dtype=F64) for n in lens]     # [y | x] rows, 9 more to decode
     want = [plain_recurrent_rows(s[:, width:], s[:, :width], w) for s in seqs]
@@ -113,11 +113,11 @@ def test_convolution_gates_and_scan(K, width, blocks, taps):
 
 @pytest.mark.parametrize("width,blocks,taps", [(30, 3, 4), (128, 8, 2), (44, 1, 1), (60, 2, 6)])
 def test_portions_and_a_slot_used_again(K, width, blocks, taps):
-    """A sequence fed in portions of 2, 7, 1, 3 and 19 tokens gives what it gives whole; then another sequence in
+    """A sequence fed in portions of 2, 7, 1, 3, 19 and 70 tokens gives what it gives whole; then another sequence in
     the same slot, once its rows are zero again, knows nothing of the first."""
     w = recurrent_weights(width, blocks, taps, 3 * width)
     g = torch.Generator().manual_seed(11)
-    for round_, n_total in enumerate((32, 32)):
+    for round_, n_total in enumerate((102, 102)):
         rows = torch.randn(n_total, 2 * width, generator=g, dtype=F64)
         ru, rS, ry = plain_recurrent_rows(rows[:, width:], rows[:, :width], w)
         if round_ == 0:
@@ -125,7 +125,7 @@ def test_portions_and_a_slot_used_again(K, width, blocks, taps):
         else:
             state[1] = 0.0
         at = 0
-        for n in (2, 7, 1, 3, 19):
+        for n in (2, 7, 1, 3, 19, 70):       # (the last portion: many rows that begin in the slot's history)
             u, y = run_recurrent_step(K, w, rows[at:at + n].float().to(DEV), batch_of([n], [1], [at]), state,
                                       torch.float32, torch.float32)
             close(u, ru[at:at + n], 2e-6)
