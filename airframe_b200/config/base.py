@@ -152,10 +152,15 @@ class ModelSpec:
     head: PartSpec
     stop_token_ids: list = field(default_factory=list)
     junctions: list = field(default_factory=list)      # PartSpecs of category ``junction``
+    # copies of the residual stream that the layers keep side by side ([tokens, streams * hidden]): all equal to the
+    # embedding's output at the start, summed before the final norm; the blocks must be of a kind that knows of them
+    streams: int = 1
 
     def validate(self) -> None:
         if not self.layers:
             raise ConfigError("a model needs at least one layer")
+        if self.streams < 1 or (self.streams > 1 and self.junctions):
+            raise ConfigError("a model has at least one residual stream (several streams and junctions do not go together)")
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ConfigError(f"schedule entry {i} names layer {e.layer} of {len(self.layers)}")

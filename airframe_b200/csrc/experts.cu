@@ -1,6 +1,8 @@
 // A routed feed-forward (mixture of experts) without a word read back by the host:
 //   expert_route   per token the router's logits in 32 bits, a score per expert (the sigmoid of its logit), the `top`
-//                  experts with the largest scores (equal scores: the lower index) and their scores; also the
+//                  experts with the largest scores (equal scores: the lower index) and their scores (optionally: a
+//                  correction added to the scores for the choice only, a choice among the best groups of experts,
+//                  weights divided by their sum and scaled); also the
 //                  sigmoid of one more row of the router matrix when there is one (the gate of a shared expert);
 //   expert_plan    the (token, choice) pairs sorted by expert: a permutation, and a table of tiles of up to 32
 //                  pairs of one expert each;
@@ -86,26 +88,71 @@ expert_score_kernel(float* __restrict__ scores, const TX* __restrict__ h, const 
   }
 }
 
-// A warp a token: the `top` largest scores in turn (equal scores: the lower index), each struck out once chosen.
+// A warp a token: the `top` largest choice scores in turn (equal scores: the lower index), each struck out once
+// chosen.  The choice score is the score plus `correction[e]` (none: the score); the weight is always the score
+// itself.  With `groups` > 1 the experts form that many equal groups of neighbours, a group's score is the sum of its
+// two largest choice scores (of its only one, in groups of one), and only experts of the `keep` best groups (equal
+// scores: the lower group) can be chosen.  With `normalise` the chosen weights are divided by their sum + 1e-20;
+// all weights are multiplied by `out_scale`.
 __global__ void __launch_bounds__(128)
 expert_choose_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ shared_gate,
-                     const float* __restrict__ scores, int n_tokens, int n_experts, int rows, int top) {
+                     const float* __restrict__ scores, const float* __restrict__ correction, int n_tokens,
+                     int n_experts, int rows, int top, int groups, int keep, int normalise, float out_scale) {
   pdl_launch_dependents();
-  extern __shared__ float score_all[];              // a row of n_experts scores a warp
+  extern __shared__ float score_all[];              // a warp: n_experts choice scores, n_experts scores, `groups` group scores
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x * (blockDim.x >> 5) + warp;
   pdl_wait();
   if (t >= n_tokens) return;
   scores = pdl_fresh(scores);
-  float* score = score_all + (size_t)warp * n_experts;
-  for (int e = lane; e < n_experts; e += 32) score[e] = scores[(size_t)t * rows + e];
+  float* choice = score_all + (size_t)warp * (2 * n_experts + groups);
+  float* score = choice + n_experts;
+  float* gscore = score + n_experts;
+  const float OUT = -3.0e38f;                       // an expert of a group that is not kept (it still beats a struck one)
+  const float STRUCK = -INFINITY;
+  for (int e = lane; e < n_experts; e += 32) {
+    const float sc = scores[(size_t)t * rows + e];
+    score[e] = sc;
+    choice[e] = sc + (correction != nullptr ? correction[e] : 0.f);
+  }
   if (shared_gate != nullptr && lane == 0) shared_gate[t] = scores[(size_t)t * rows + n_experts];
   __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int per = n_experts / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float a = STRUCK, b = STRUCK;                 // the two largest of the group
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float c = choice[e];
+        if (c > a) b = a, a = c;
+        else if (c > b) b = c;
+      }
+      gscore[g] = per > 1 ? a + b : a;
+    }
+    __syncwarp();
+    for (int k = 0; k < keep; ++k) {                // the best groups in turn, marked by +infinity
+      float best = STRUCK;
+      int at = groups;
+      for (int g = lane; g < groups; g += 32)
+        if (gscore[g] != INFINITY && gscore[g] > best) best = gscore[g], at = g;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ob > best || (ob == best && oa < at)) best = ob, at = oa;
+      }
+      if (lane == 0 && at < groups) gscore[at] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < n_experts; e += 32)
+      if (gscore[e / per] != INFINITY) choice[e] = OUT;
+    __syncwarp();
+  }
+  float total = 0.f;                                // (lane 0's)
   for (int k = 0; k < top; ++k) {
-    float best = -1.f;                              // (a sigmoid is never negative; a chosen expert's score is set to -2)
+    float best = STRUCK;
     int at = n_experts;
     for (int e = lane; e < n_experts; e += 32)
-      if (score[e] > best) best = score[e], at = e; // (ascending e: the lower index wins among equals)
+      if (choice[e] > best) best = choice[e], at = e; // (ascending e: the lower index wins among equals)
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
@@ -113,22 +160,34 @@ expert_choose_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __re
       if (ob > best || (ob == best && oa < at)) best = ob, at = oa;
     }
     if (lane == 0) {
+      if (at >= n_experts) at = 0;                  // (cannot be: top <= n_experts, and every expert's choice score is finite)
       ids[(size_t)t * top + k] = at;
-      wts[(size_t)t * top + k] = best;
-      score[at] = -2.f;
+      wts[(size_t)t * top + k] = score[at];
+      total += score[at];
+      choice[at] = STRUCK;
     }
     __syncwarp();
+  }
+  if (lane == 0) {
+    const float f = normalise ? out_scale / (total + 1e-20f) : out_scale;
+    if (normalise || out_scale != 1.f)
+      for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= f;
   }
 }
 
 // scores: room for n_tokens x (n_experts + 1) floats.
 AF_EXPORT int af_expert_route(int* ids, float* wts, float* shared_gate, float* scores, const void* h, int h_dtype,
                               const float* router, int n_tokens, int hidden, int n_experts, int top,
+                              const float* correction, int groups, int keep, int normalise, float out_scale,
                               cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   AF_REQUIRE(n_tokens > 0 && hidden > 0 && n_experts > 0 && top >= 1 && top <= n_experts && scores != nullptr,
              "af_expert_route: %d of %d experts", top, n_experts);
   AF_REQUIRE(n_experts <= 8192, "af_expert_route: up to 8192 experts");
+  if (groups < 1) groups = 1;
+  AF_REQUIRE(n_experts % groups == 0 && keep >= 1 && keep <= groups && (long long)keep * (n_experts / groups) >= top,
+             "af_expert_route: %d experts in %d groups of which %d are kept cannot give %d choices", n_experts, groups,
+             keep, top);
   const int rows = n_experts + (shared_gate != nullptr ? 1 : 0);
   // a prompt: four tokens a warp (a row of the router is read once for them); few tokens: a warp each
   const int tm = n_tokens >= 256 ? 4 : 1;
@@ -145,10 +204,10 @@ AF_EXPORT int af_expert_route(int* ids, float* wts, float* shared_gate, float* s
                                 (const TX*)h, router, n_tokens, hidden, rows));
   }
   AF_COUNT_LAUNCH("af_expert_route");
-  const int warps = n_experts <= 2048 ? 4 : 1;
+  const int warps = n_experts <= 1024 ? 4 : 1;
   af_launch(expert_choose_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps),
-            (size_t)warps * n_experts * sizeof(float), stream, ids, wts, shared_gate, (const float*)scores, n_tokens,
-            n_experts, rows, top);
+            (size_t)warps * (2 * n_experts + groups) * sizeof(float), stream, ids, wts, shared_gate, (const float*)scores,
+            correction, n_tokens, n_experts, rows, top, groups, keep, normalise, out_scale);
   AF_CHECK_LAUNCH("af_expert_route");
 }
 
@@ -255,15 +314,19 @@ __device__ __forceinline__ float clamped_glu(float g, float u, float limit) {
 // DUAL: out[sorted row][n] = act(s (x . w0[e][n]), s (x . w1[e][n])) * post, x the row of `a` that the pair's
 //       token names, s the pair's weight (a weight on an expert's input goes through its products, which have no
 //       bias), post the token's `scale_out` (1 without); out of the compute dtype, rows of N values.
+// MODE 2: out[sorted row][n] = gelu(x . w0[e][n]) * s * post with the exact (erf) GELU: an expert of one matrix, whose
+//       weight stands behind the activation.
 // else: out[(choice, token)][n] = a[sorted row] . w0[e][n] as floats: [top][tokens][N], partial sums that the
 //       residual kernel adds.
 // Without a plan (plan == nullptr) there is one expert and the rows are the tokens in order.
-template <typename T, bool DUAL>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 expert_rows_kernel(void* __restrict__ out_, const T* __restrict__ a, const T* __restrict__ w0, const T* __restrict__ w1,
                    const int* __restrict__ perm, const int* __restrict__ plan, const float* __restrict__ pair_weight,
                    const float* __restrict__ scale_out, int n_rows, int n_tokens, int top, int N, int K, float limit) {
   pdl_launch_dependents();
+  constexpr bool DUAL = MODE == 1;                  // gate and up with the clamped activation
+  constexpr bool MID = MODE != 0;                   // rows out in sorted order, of the compute dtype (MODE 2: one matrix, exact GELU)
   __shared__ float as[AF_EX_TM][AF_EX_TK];
   __shared__ float w0s[AF_EX_TN][AF_EX_TK + 1];
   __shared__ float w1s[DUAL ? AF_EX_TN : 1][AF_EX_TK + 1];
@@ -286,7 +349,7 @@ expert_rows_kernel(void* __restrict__ out_, const T* __restrict__ a, const T* __
     int pair = -1;
     if (m < rows) pair = perm != nullptr ? perm[row0 + m] : row0 + m;
     pair_of[m] = pair;
-    src_row[m] = pair < 0 ? -1 : (DUAL ? pair / top : row0 + m);
+    src_row[m] = pair < 0 ? -1 : (MID ? pair / top : row0 + m);
   }
   __syncthreads();
   const T* w0e = w0 + (size_t)expert * N * K;
@@ -327,10 +390,12 @@ expert_rows_kernel(void* __restrict__ out_, const T* __restrict__ a, const T* __
     const int row = ty + 4 * m;
     const int pair = pair_of[row];
     if (pair < 0) continue;
-    if (DUAL) {
+    if (MID) {
       const float s = pair_weight != nullptr ? pair_weight[pair] : 1.f;
       const float post = scale_out != nullptr ? scale_out[pair / top] : 1.f;
-      static_cast<T*>(out_)[(size_t)(row0 + row) * N + n] = from_f32<T>(clamped_glu(s * acc0[m], s * acc1[m], limit) * post);
+      const float val = DUAL ? clamped_glu(s * acc0[m], s * acc1[m], limit) * post
+                             : 0.5f * acc0[m] * (1.f + erff(acc0[m] * 0.70710678118654752f)) * s * post;
+      static_cast<T*>(out_)[(size_t)(row0 + row) * N + n] = from_f32<T>(val);
     } else {
       const int token = pair / top, choice = pair % top;
       static_cast<float*>(out_)[((size_t)choice * n_tokens + token) * N + n] = acc0[m];
@@ -340,7 +405,8 @@ expert_rows_kernel(void* __restrict__ out_, const T* __restrict__ a, const T* __
 
 AF_EXPORT int af_expert_rows(void* out, const void* a, const void* w0, const void* w1, int dtype, const int* perm,
                              const int* plan, const float* pair_weight, const float* scale_out, int n_rows,
-                             int n_tokens, int top, int max_tiles, int N, int K, float limit, cudaStream_t stream) {
+                             int n_tokens, int top, int max_tiles, int N, int K, float limit, int act,
+                             cudaStream_t stream) {
   if (n_rows == 0) return 0;
   AF_REQUIRE(n_rows > 0 && n_tokens > 0 && top >= 1 && N > 0 && K > 0, "af_expert_rows: bad sizes");
   AF_REQUIRE((plan == nullptr) == (perm == nullptr), "af_expert_rows: a plan and its permutation, or neither");
@@ -351,11 +417,15 @@ AF_EXPORT int af_expert_rows(void* out, const void* a, const void* w0, const voi
   AF_REQUIRE(grid.y < 65536, "af_expert_rows: too many outputs");
   if (w1 != nullptr) {
     AF_DISPATCH_DTYPE(dtype, T,
-                      af_launch(expert_rows_kernel<T, true>, grid, dim3(256), 0, stream, out, (const T*)a, (const T*)w0,
+                      af_launch(expert_rows_kernel<T, 1>, grid, dim3(256), 0, stream, out, (const T*)a, (const T*)w0,
                                 (const T*)w1, perm, plan, pair_weight, scale_out, n_rows, n_tokens, top, N, K, limit));
+  } else if (act == 1) {
+    AF_DISPATCH_DTYPE(dtype, T,
+                      af_launch(expert_rows_kernel<T, 2>, grid, dim3(256), 0, stream, out, (const T*)a, (const T*)w0,
+                                (const T*)nullptr, perm, plan, pair_weight, scale_out, n_rows, n_tokens, top, N, K, limit));
   } else {
     AF_DISPATCH_DTYPE(dtype, T,
-                      af_launch(expert_rows_kernel<T, false>, grid, dim3(256), 0, stream, out, (const T*)a, (const T*)w0,
+                      af_launch(expert_rows_kernel<T, 0>, grid, dim3(256), 0, stream, out, (const T*)a, (const T*)w0,
                                 (const T*)nullptr, perm, plan, pair_weight, scale_out, n_rows, n_tokens, top, N, K, limit));
   }
   AF_CHECK_LAUNCH("af_expert_rows");

@@ -64,7 +64,8 @@ struct ExArgs {
   const float* rate;
 };
 
-enum { EX_DOWN = 0, EX_ACT = 1, EX_GATES = 2 };
+enum { EX_DOWN = 0, EX_ACT = 1, EX_GATES = 2, EX_GELU = 3 };
+__host__ __device__ constexpr int ex_accs(int epi) { return epi == EX_ACT || epi == EX_GATES ? 2 : 1; }
 
 __device__ __forceinline__ float ex_act(float g, float u, float limit) {
   g = fminf(g, limit);
@@ -97,9 +98,10 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(EX_THREADS, BN <= 64 ? 2 : 1)
 expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
                       const __grid_constant__ CUtensorMap map_x, ExArgs a) {
-  constexpr bool DUAL = EPI != EX_DOWN;
+  constexpr bool DUAL = ex_accs(EPI) == 2;
   constexpr bool GATES = EPI == EX_GATES;
-  constexpr int NACC = DUAL ? 2 : 1;
+  constexpr bool SINGLE = EPI == EX_GELU;        // one matrix with the exact GELU behind it, rows out like DUAL's
+  constexpr int NACC = ex_accs(EPI);
   constexpr int XB = BN < 64 ? BN : 64;          // rows of a box of the input rows: a tile fetches as many boxes as hold its rows
   constexpr int STAGES = ex_stages(BN, NACC);
   constexpr int A_BYTES = EX_BM * EX_BK * 2;
@@ -269,7 +271,7 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_c
         float s_l = 1.f, post_l = 1.f;
         int dst_l = -1;                                   // (DOWN: the row of out, top * n_tokens of them)
         if (pair >= 0) {
-          if constexpr (DUAL) {
+          if constexpr (DUAL || SINGLE) {
             if (a.pair_weight != nullptr) s_l = __ldcg(a.pair_weight + pair);
             if (a.scale_out != nullptr) post_l = __ldcg(a.scale_out + pair / a.top);
           } else {
@@ -284,7 +286,7 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_c
           if (lane == 0) mbar_arrive(&acc_empty);
         }
         const int n = min(CW, rows - c0);                 // (sorted rows: the chunk's first n are the tile's)
-        if constexpr (DUAL) {
+        if constexpr (DUAL || SINGLE) {
           const bool scaled = a.pair_weight != nullptr, posted = a.scale_out != nullptr;
           __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.out) + (size_t)(row0 + c0) * a.N + f;
 #pragma unroll
@@ -292,7 +294,10 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_c
             const float s = scaled ? __shfl_sync(0xffffffffu, s_l, j) : 1.f;
             const float post = posted ? __shfl_sync(0xffffffffu, post_l, j) : 1.f;
             if (j >= n || f >= a.N) continue;
-            o[(size_t)j * a.N] = __float2bfloat16_rn(ex_act(s * g[j], s * u[j], a.limit) * post);
+            if constexpr (SINGLE)       // (the weight stands behind the activation: it is the expert's output that is weighed)
+              o[(size_t)j * a.N] = __float2bfloat16_rn(0.5f * g[j] * (1.f + erff(g[j] * 0.70710678118654752f)) * s * post);
+            else
+              o[(size_t)j * a.N] = __float2bfloat16_rn(ex_act(s * g[j], s * u[j], a.limit) * post);
           }
         } else {
 #pragma unroll
@@ -320,7 +325,7 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_c
 
 template <int BN, int EPI>
 int ex_launch(const CUtensorMap& m0, const CUtensorMap& m1, const CUtensorMap& mx, const ExArgs& a, cudaStream_t stream) {
-  constexpr int NACC = EPI != EX_DOWN ? 2 : 1;
+  constexpr int NACC = ex_accs(EPI);
   constexpr int smem = ex_stages(BN, NACC) * ex_stage_bytes(BN, NACC) + 1024;
   static bool configured[AF_MAX_DEVICES] = {};
   const int dev = af_current_device();
@@ -356,11 +361,12 @@ int ex_launch_bn(int bn, const CUtensorMap& m0, const CUtensorMap& m1, const CUt
 // The sorted rows' products on the tensor cores.  a [n_rows, K] bfloat16 in sorted order (w1 given: the rows that
 // the pairs' tokens name, gathered; else the first product's output); w0, w1 [experts, N, K] bfloat16; tile: the
 // plan's row tile (16, 32, 64, 128 or 256; at most so many rows a plan entry).  K a multiple of 8, bases 16-byte
-// aligned.  Otherwise as af_expert_rows.
+// aligned.  act 1 (no w1): out[sorted row] = gelu(a w0[e]^T) * s * post with the exact (erf) GELU, rows of the
+// compute dtype like the two-matrix form's.  Otherwise as af_expert_rows.
 AF_EXPORT int af_expert_rows_tc(void* out, const void* a, const void* w0, const void* w1, int n_experts, const int* perm,
                                 const int* plan, const float* pair_weight, const float* scale_out, int n_rows,
-                                int n_tokens, int top, int max_tiles, int tile, int N, int K, float limit, int* err,
-                                cudaStream_t stream) {
+                                int n_tokens, int top, int max_tiles, int tile, int N, int K, float limit, int act,
+                                int* err, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   AF_REQUIRE(n_rows > 0 && n_tokens > 0 && top >= 1 && N > 0 && K > 0 && n_experts > 0, "af_expert_rows_tc: bad sizes");
   AF_REQUIRE((plan == nullptr) == (perm == nullptr), "af_expert_rows_tc: a plan and its permutation, or neither");
@@ -380,7 +386,9 @@ AF_EXPORT int af_expert_rows_tc(void* out, const void* a, const void* w0, const 
   ExArgs args{out, N, K, n_rows, n_tokens, top, (N + EX_BM - 1) / EX_BM,
               plan != nullptr ? max_tiles : (n_rows + tile - 1) / tile, perm, plan, pair_weight, scale_out, limit, err};
   AF_REQUIRE(args.max_row_tiles > 0, "af_expert_rows_tc: no tiles");
+  AF_REQUIRE(act == 0 || (act == 1 && w1 == nullptr), "af_expert_rows_tc: the exact GELU stands behind one matrix");
   if (w1 != nullptr) return ex_launch_bn<EX_ACT>(tile, m0, m1, mx, args, stream);
+  if (act == 1) return ex_launch_bn<EX_GELU>(tile, m0, m1, mx, args, stream);
   return ex_launch_bn<EX_DOWN>(tile, m0, m1, mx, args, stream);
 }
 

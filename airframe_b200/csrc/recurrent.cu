@@ -80,7 +80,7 @@ AF_EXPORT int af_delta_prep(float* out, const float* proj, long long ld, int off
 
 // ---------------------------------------------------------------- the scan over a matrix state
 
-enum AfScanMode { AF_SCAN_DECAY = 0, AF_SCAN_DELTA = 1 };
+enum AfScanMode { AF_SCAN_DECAY = 0, AF_SCAN_DELTA = 1, AF_SCAN_CHANNEL = 3 };
 // (inside the library: the decay recurrence whose r, k and v pass through SiLU as they are read; a kernel of
 // its own, so that the others carry no exponentials)
 #define AF_SCAN_DECAY_SILU 2
@@ -89,6 +89,7 @@ enum AfScanMode { AF_SCAN_DECAY = 0, AF_SCAN_DELTA = 1 };
 // tokens in elements; head h's piece starts h * dk (h * dv for v) behind the pointer):
 //   DECAY:  S <- decay[h] S + k v^T                          o = S^T q     (q = `r`)
 //   DELTA:  S <- diag(w) S - au (u^T S) + k v^T              o = S^T r     (decay and removal act on the S before the token)
+//   CHANNEL: S <- diag(w) S + k v^T                          o = S^T q     (a decay per key channel and token, no removal)
 // With `silu` the r, k and v values go through x / (1 + exp(-x)) as they are read.
 struct AfScanArgs {
   const float *r, *k, *v, *w, *u, *au;
@@ -133,7 +134,7 @@ state_scan_kernel(AfScanArgs a) {
   constexpr bool SILU = MODE == AF_SCAN_DECAY_SILU;
   extern __shared__ __align__(16) float smem[];
   const int P = a.lanes, CT = a.cols, CH = a.chunk, dk = a.dk, dv = a.dv;
-  const int NV = MODE == AF_SCAN_DELTA ? 5 : 2;             // staged key-sized vectors: r, k (, w, u, au)
+  const int NV = MODE == AF_SCAN_DELTA ? 5 : MODE == AF_SCAN_CHANNEL ? 3 : 2;   // staged key-sized vectors: r, k (, w (, u, au))
   const int dkp = P * (R + AF_SCAN_PAD(R));
   const int tok_floats = NV * dkp + CT;                     // a token's staged floats: the vectors, then its v tile
   const int buf_floats = CH * tok_floats;
@@ -167,7 +168,7 @@ state_scan_kernel(AfScanArgs a) {
 #pragma unroll
     for (int i = 0; i < R; ++i) S[i] = (col_on && part * R + i < dk) ? st[i] : 0.f;
   }
-  const float dec = MODE != AF_SCAN_DELTA ? a.decay[h] : 0.f;
+  const float dec = (MODE == AF_SCAN_DECAY || MODE == AF_SCAN_DECAY_SILU) ? a.decay[h] : 0.f;
   auto keep_state = [&]() {
     if (!col_on) return;
     if (vec) {
@@ -321,6 +322,13 @@ state_scan_kernel(AfScanArgs a) {
         const float dot = lanes_sum(d0 + d1, P);
 #pragma unroll
         for (int i = 0; i < R; ++i) S[i] = wv[i] * S[i] - av[i] * dot + kv[i] * vj;
+      } else if (MODE == AF_SCAN_CHANNEL) {
+        float wv[R];
+#pragma unroll
+        for (int i = 0; i < R; i += 4)
+          *reinterpret_cast<float4*>(wv + i) = *reinterpret_cast<const float4*>(tk + 2 * dkp + i);
+#pragma unroll
+        for (int i = 0; i < R; ++i) S[i] = wv[i] * S[i] + kv[i] * vj;
       } else {
 #pragma unroll
         for (int i = 0; i < R; ++i) S[i] = dec * S[i] + kv[i] * vj;
@@ -377,7 +385,7 @@ state_step_kernel(AfScanArgs a, int vec) {
 #pragma unroll
     for (int i = 0; i < R; ++i) S[i] = (col_on && c0 + i < dk) ? st[i] : 0.f;
   }
-  const float dec = MODE != AF_SCAN_DELTA ? a.decay[h] : 0.f;
+  const float dec = (MODE == AF_SCAN_DECAY || MODE == AF_SCAN_DECAY_SILU) ? a.decay[h] : 0.f;
   pdl_wait();
   auto piece = [&](const float* p, float* dst, bool act) {
     p += h * dk + c0;
@@ -413,6 +421,11 @@ state_step_kernel(AfScanArgs a, int vec) {
     const float dot = lanes_sum(d0 + d1, P);
 #pragma unroll
     for (int i = 0; i < R; ++i) S[i] = wv[i] * S[i] - av[i] * dot + kv[i] * vj;
+  } else if (MODE == AF_SCAN_CHANNEL) {
+    float wv[R];
+    piece(a.w + t * a.w_ts, wv, false);
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] = wv[i] * S[i] + kv[i] * vj;
   } else {
 #pragma unroll
     for (int i = 0; i < R; ++i) S[i] = dec * S[i] + kv[i] * vj;
@@ -437,6 +450,7 @@ state_step_kernel(AfScanArgs a, int vec) {
 template <int R>
 static int launch_step(const AfScanArgs& a, int mode, int vec, dim3 grid, int threads, cudaStream_t stream) {
   if (mode == AF_SCAN_DELTA) af_launch(state_step_kernel<R, AF_SCAN_DELTA>, grid, dim3(threads), 0, stream, a, vec);
+  else if (mode == AF_SCAN_CHANNEL) af_launch(state_step_kernel<R, AF_SCAN_CHANNEL>, grid, dim3(threads), 0, stream, a, vec);
   else if (a.silu) af_launch(state_step_kernel<R, AF_SCAN_DECAY_SILU>, grid, dim3(threads), 0, stream, a, vec);
   else af_launch(state_step_kernel<R, AF_SCAN_DECAY>, grid, dim3(threads), 0, stream, a, vec);
   AF_CHECK_LAUNCH("af_state_scan");
@@ -444,22 +458,24 @@ static int launch_step(const AfScanArgs& a, int mode, int vec, dim3 grid, int th
 
 template <int R, bool VEC>
 static int launch_scan(const AfScanArgs& a, int mode, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
-  static bool raised[3][AF_MAX_DEVICES];
+  static bool raised[4][AF_MAX_DEVICES];
   auto k0 = state_scan_kernel<R, AF_SCAN_DECAY, VEC>;
   auto k1 = state_scan_kernel<R, AF_SCAN_DELTA, VEC>;
   auto k2 = state_scan_kernel<R, AF_SCAN_DECAY_SILU, VEC>;
-  const int which = mode == AF_SCAN_DELTA ? 1 : (a.silu ? 2 : 0);
+  auto k3 = state_scan_kernel<R, AF_SCAN_CHANNEL, VEC>;
+  const int which = mode == AF_SCAN_DELTA ? 1 : mode == AF_SCAN_CHANNEL ? 3 : (a.silu ? 2 : 0);
   if (smem > 48 * 1024) {
     const int dev = af_current_device();
     if (dev < 0) return -1;
     if (af_first_on_device(raised[which], dev)) {
-      cudaError_t e = cudaFuncSetAttribute(which == 1 ? k1 : which == 2 ? k2 : k0, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t e = cudaFuncSetAttribute(which == 1 ? k1 : which == 2 ? k2 : which == 3 ? k3 : k0, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            96 * 1024);
       if (e != cudaSuccess) return af_fail((int)e, "af_state_scan: %s", cudaGetErrorString(e));
     }
   }
   if (which == 1) af_launch(k1, grid, dim3(threads), smem, stream, a);
   else if (which == 2) af_launch(k2, grid, dim3(threads), smem, stream, a);
+  else if (which == 3) af_launch(k3, grid, dim3(threads), smem, stream, a);
   else af_launch(k0, grid, dim3(threads), smem, stream, a);
   AF_CHECK_LAUNCH("af_state_scan");
 }
@@ -481,7 +497,7 @@ static void scan_cut(int mode, int dk, int dv, bool vec, long long units, int wa
   // (few blocks a head, many warps a block) cost less than narrow ones, also where that leaves SMs without a block
   int ct = 256 / p;
   while (ct > 4 && ct / 2 >= dv && (ct / 2) * p >= 32) ct /= 2;   // (no wider than the state's columns need; whole warps)
-  const int nv = mode == AF_SCAN_DELTA ? 5 : 2;
+  const int nv = mode == AF_SCAN_DELTA ? 5 : mode == AF_SCAN_CHANNEL ? 3 : 2;
   const int tok_vals = nv * dk + ct, tok_floats = nv * p * (r + AF_SCAN_PAD(r)) + ct;
   const int threads = ct * p;
   int ch = 16;
@@ -500,8 +516,8 @@ AF_EXPORT int af_state_scan(int mode, const float* r, long long r_ts, const floa
                             long long out_ts, const int* seq_starts, const int* slots, int n_seqs, int n_tokens, int heads,
                             int dk, int dv, int silu, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
-  AF_REQUIRE(mode == AF_SCAN_DECAY || mode == AF_SCAN_DELTA, "af_state_scan: mode %d", mode);
-  AF_REQUIRE(!(mode == AF_SCAN_DELTA && silu), "af_state_scan: the delta rule takes its vectors as they are");
+  AF_REQUIRE(mode == AF_SCAN_DECAY || mode == AF_SCAN_DELTA || mode == AF_SCAN_CHANNEL, "af_state_scan: mode %d", mode);
+  AF_REQUIRE(!(mode != AF_SCAN_DECAY && silu), "af_state_scan: only the plain decay takes its vectors through SiLU");
   AF_REQUIRE(n_seqs > 0 && heads > 0 && dk > 0 && dv > 0 && dk <= 1024, "af_state_scan: bad sizes (key size up to 1024)");
   AF_REQUIRE(n_seqs < 65536 && heads < 65536, "af_state_scan: too many sequences or heads for one grid");
   AfScanArgs a;
@@ -512,6 +528,7 @@ AF_EXPORT int af_state_scan(int mode, const float* r, long long r_ts, const floa
   // whole 16-byte pieces: sizes and strides in multiples of four floats, bases on 16 bytes
   bool vec = dk % 4 == 0 && dv % 4 == 0 && ((r_ts | k_ts | v_ts) & 3) == 0 &&
              (((uintptr_t)r | (uintptr_t)k | (uintptr_t)v) & 15) == 0;
+  if (mode == AF_SCAN_CHANNEL) vec = vec && (w_ts & 3) == 0 && ((uintptr_t)w & 15) == 0;
   if (mode == AF_SCAN_DELTA)
     vec = vec && ((w_ts | u_ts | au_ts) & 3) == 0 && (((uintptr_t)w | (uintptr_t)u | (uintptr_t)au) & 15) == 0;
   const int sms = af_sm_count();
@@ -519,7 +536,7 @@ AF_EXPORT int af_state_scan(int mode, const float* r, long long r_ts, const floa
   int R, P, CT, CH;
   scan_cut(mode, dk, dv, vec, (long long)heads * n_seqs, sms, &R, &P, &CT, &CH);
   AF_REQUIRE(P * R >= dk, "af_state_scan: key size %d does not fit %d lanes of %d", dk, P, R);
-  const int nv = mode == AF_SCAN_DELTA ? 5 : 2;
+  const int nv = mode == AF_SCAN_DELTA ? 5 : mode == AF_SCAN_CHANNEL ? 3 : 2;
   if (vec)
     AF_REQUIRE(CH * (dk / 4) <= AF_SCAN_VEC_ITEMS * CT * P && CH * (CT / 4) <= AF_SCAN_VEC_ITEMS * CT * P,
                "af_state_scan: a token of %d values is too long to stage", nv * dk + CT);
@@ -557,47 +574,52 @@ AF_EXPORT int af_state_scan(int mode, const float* r, long long r_ts, const floa
 
 // ---------------------------------------------------------------- the output of a state mixer
 
-// y[t][i] = o[t][i] * rsqrt(mean over i's group of o^2 + eps) * w[i] * sigmoid(gate[t][i]): a norm over groups
-// of `group` values (a head, or the whole row) with a weight vector (no offset), times a gate.  One block per token.
+// y[t][i] = o'[t][i] * rsqrt(mean over i's group of o'^2 + eps) * w[i] * sigmoid(gate[t][i]), o' = in_scale * o: a norm
+// over groups of `group` values (a head, or the whole row) with a weight vector (no offset), times a gate (its sigmoid,
+// or with gate_act 1 the gate times its sigmoid).  One block per token.
 template <typename TY>
 __global__ void __launch_bounds__(256)
 gated_group_norm_kernel(TY* __restrict__ y, const float* __restrict__ o, const float* __restrict__ w,
-                        const float* __restrict__ gate, long long gate_ts, int n, int group, float eps) {
+                        const float* __restrict__ gate, long long gate_ts, int n, int group, float eps, int gate_act,
+                        float in_scale) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[33];
+  // the gate: its sigmoid, or (gate_act 1) the gate itself times its sigmoid
+  auto gated = [&](float g) { const float sg = 1.f / (1.f + expf(-g)); return gate_act ? g * sg : sg; };
   const int t = blockIdx.x;
   const float* orow = o + (size_t)t * n;
   const float* grow = gate + (size_t)t * gate_ts;
   TY* yrow = y + (size_t)t * n;
   if (group == n) {
     float ss = 0.f;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += orow[i] * orow[i];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += (orow[i] * in_scale) * (orow[i] * in_scale);
     ss = block_sum(ss, scratch);
     const float inv = rsqrtf(ss / (float)n + eps);
     for (int i = threadIdx.x; i < n; i += blockDim.x)
-      yrow[i] = from_f32<TY>(orow[i] * inv * w[i] * (1.f / (1.f + expf(-grow[i]))));
+      yrow[i] = from_f32<TY>(orow[i] * in_scale * inv * w[i] * gated(grow[i]));
     return;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   for (int g = warp; g < n / group; g += nwarp) {
     float ss = 0.f;
-    for (int c = lane; c < group; c += 32) ss += orow[g * group + c] * orow[g * group + c];
+    for (int c = lane; c < group; c += 32) ss += (orow[g * group + c] * in_scale) * (orow[g * group + c] * in_scale);
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / (float)group + eps);
     for (int c = lane; c < group; c += 32) {
       const int i = g * group + c;
-      yrow[i] = from_f32<TY>(orow[i] * inv * w[i] * (1.f / (1.f + expf(-grow[i]))));
+      yrow[i] = from_f32<TY>(orow[i] * in_scale * inv * w[i] * gated(grow[i]));
     }
   }
 }
 
 AF_EXPORT int af_gated_group_norm(void* y, int y_dtype, const float* o, const float* w, const float* gate,
-                                  long long gate_ts, int n_tokens, int n, int group, float eps, cudaStream_t stream) {
+                                  long long gate_ts, int n_tokens, int n, int group, float eps, int gate_act,
+                                  float in_scale, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   AF_REQUIRE(n_tokens > 0 && n > 0 && group > 0 && n % group == 0, "af_gated_group_norm: %d values in groups of %d", n, group);
   AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(gated_group_norm_kernel<TY>, dim3(n_tokens), dim3(256), 0, stream, (TY*)y, o, w,
-                                           gate, gate_ts, n, group, eps));
+                                           gate, gate_ts, n, group, eps, gate_act, in_scale));
   AF_CHECK_LAUNCH("af_gated_group_norm");
 }
 
@@ -687,4 +709,40 @@ AF_EXPORT int af_gated_scan(void* y, int y_dtype, const float* proj, long long l
   AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(gated_scan_kernel<TY>, dim3((width + 31) / 32, n_seqs), dim3(AF_GS_WARPS * 32), 0, stream,
                                            (TY*)y, proj, ld, off_z, off_x, off_g, bz, bx, state, seq_starts, slots, width));
   AF_CHECK_LAUNCH("af_gated_scan");
+}
+
+// ---------------------------------------------------------------- decays of gated linear attention
+
+// alpha[t][c] = sigmoid(z)^(1 / tau), z = b[c] + sum_r w2t[r][c] * low[t][r], with low the `rank` columns of the packed
+// float32 projection rows that begin at off_low (the first factor of a low-rank pair, applied with the other
+// projections), w2t [rank, n] the second factor transposed.  Worked out as exp(log(sigmoid(z)) / tau) with
+// log(sigmoid(z)) = min(z, 0) - log1p(exp(-|z|)): 32-bit throughout, no underflow of the sigmoid on the way.
+// One block per token; the token's low-rank row lies in shared memory.
+__global__ void __launch_bounds__(256)
+channel_decay_kernel(float* __restrict__ alpha, const float* __restrict__ proj, long long ld, int off_low,
+                     const float* __restrict__ w2t, const float* __restrict__ bias, int rank, int n, float inv_tau) {
+  pdl_launch_dependents();
+  extern __shared__ float low[];
+  const size_t t = blockIdx.x;
+  pdl_wait();
+  proj = pdl_fresh(proj);
+  for (int r = threadIdx.x; r < rank; r += blockDim.x) low[r] = proj[t * ld + off_low + r];
+  __syncthreads();
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float z = 0.f;
+    for (int r = 0; r < rank; ++r) z = fmaf(w2t[(size_t)r * n + c], low[r], z);
+    z += bias[c];
+    const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+    alpha[t * n + c] = expf(ls * inv_tau);
+  }
+}
+
+AF_EXPORT int af_channel_decay(float* alpha, const float* proj, long long ld, int off_low, const float* w2t,
+                               const float* bias, int rank, int n_tokens, int n, float tau, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && n > 0 && rank > 0 && rank <= 8192 && tau > 0.f, "af_channel_decay: bad sizes (rank up to 8192)");
+  const int threads = n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256;
+  af_launch(channel_decay_kernel, dim3(n_tokens), dim3(threads), (size_t)rank * sizeof(float), stream, alpha, proj, ld,
+            off_low, w2t, bias, rank, n, 1.f / tau);
+  AF_CHECK_LAUNCH("af_channel_decay");
 }

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config.base import ModelSpec
+from ..config.base import ConfigError, ModelSpec
 from ..parts import BuildContext, build_part
 
 
@@ -35,6 +35,11 @@ class Model:
         self.junctions = [build_part("junction", j, self.ctx) for j in spec.junctions]
         self.final_norm = build_part("norm", spec.final_norm, self.ctx)
         self.head = build_part("head", spec.head, self.ctx)
+        self.streams = int(spec.streams)
+        for b in self.blocks:
+            if getattr(b, "streams", 1) != self.streams:
+                raise ConfigError(f"a block of kind '{b.kind}' keeps {getattr(b, 'streams', 1)} residual streams, "
+                                  f"the model {self.streams}")
         self.loaded = False
 
     # ------------------------------------------------------------------ weights
@@ -111,6 +116,11 @@ class Model:
         x = self.embedding.forward(batch.tokens)
         if probe is not None:
             probe.after(-1, -1, x, batch)
+        if self.streams > 1:         # the layers keep several copies of the stream side by side, all equal at the start
+            from .. import kernels
+            one = x
+            x = torch.empty(one.shape[0], self.streams * one.shape[1], dtype=torch.float32, device=one.device)
+            kernels.stream_copy(x, one, self.streams)
         sched = self.spec.schedule
         # a junction sees the embedding's output beside the stream (which the layers rewrite in place)
         x0 = x.clone() if any(e.enter is not None for e in sched) else None
@@ -126,8 +136,15 @@ class Model:
                 nxt = self.blocks[sched[i + 1].layer].first_norm()
             normed = blk.forward(x, batch, cache.views[i], normed=normed, next_pre=nxt)
             if probe is not None:
-                probe.after(i, e.layer, x, batch)
-        return x
+                probe.after(i, e.layer, self._sum_streams(x) if self.streams > 1 else x, batch)
+        return self._sum_streams(x) if self.streams > 1 else x
+
+    def _sum_streams(self, x) -> torch.Tensor:
+        """The model's stream: the sum of the copies the layers keep."""
+        from .. import kernels
+        out = torch.empty(x.shape[0], x.shape[1] // self.streams, dtype=torch.float32, device=x.device)
+        kernels.stream_sum(out, x, self.streams)
+        return out
 
     def logits(self, x, want_rows) -> torch.Tensor:
         """float32 logits [R, V] at the wanted rows of the residual stream."""

@@ -844,7 +844,7 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None,
 
 # ---------------------------------------------------------------- mixers with a state of fixed size
 
-SCAN_MODES = {"decay": 0, "delta": 1}
+SCAN_MODES = {"decay": 0, "delta": 1, "channel": 3}
 
 
 def _f32_rows(t, name):
@@ -882,7 +882,8 @@ def state_scan(mode: str, out, r, k, v, state, batch, heads: int, dk: int, dv: i
     the state that earlier steps left in ``state`` (float32 [slots, heads, dv, dk]; left updated):
 
     ``decay``: S <- decay[h] S + k v^T, o = S^T r;
-    ``delta``: S <- diag(w) S - au (u^T S) + k v^T, o = S^T r (the decay and the removal act on the state before the token).
+    ``delta``: S <- diag(w) S - au (u^T S) + k v^T, o = S^T r (the decay and the removal act on the state before the token);
+    ``channel``: S <- diag(w) S + k v^T, o = S^T r (a decay per key channel and token, no removal).
 
     r, k, w, u, au: float32 rows [T, heads * dk] (column sections allowed), v [T, heads * dv], out float32
     [T, heads * dv].  ``silu``: r, k and v pass through x * sigmoid(x) as they are read.  A step in which
@@ -901,6 +902,11 @@ def state_scan(mode: str, out, r, k, v, state, batch, heads: int, dk: int, dv: i
             raise KernelError("state_scan: the delta rule needs w, u and au")
         extra = [_f32_rows(t, n) for t, n in ((w, "w"), (u, "u"), (au, "au"))]
         dec = ctypes.c_void_p(0)
+    elif mode == "channel":
+        if w is None or tuple(w.shape) != (T, heads * dk):
+            raise KernelError(f"state_scan: a decay per key channel and token, [{T}, {heads * dk}]")
+        extra = [_f32_rows(w, "w"), null, null]
+        dec = ctypes.c_void_p(0)
     else:
         if decay is None or decay.numel() != heads:
             raise KernelError("state_scan: one decay per head")
@@ -914,8 +920,12 @@ def state_scan(mode: str, out, r, k, v, state, batch, heads: int, dk: int, dv: i
                                 _stream()))
 
 
-def gated_group_norm(y, o, w, gate, group: int, eps: float) -> None:
-    """y = o * rsqrt(mean over each group of ``group`` values of o^2 + eps) * w * sigmoid(gate);
+GATE_ACTS = {"sigmoid": 0, "silu": 1}
+
+
+def gated_group_norm(y, o, w, gate, group: int, eps: float, gate_act: str = "sigmoid", in_scale: float = 1.0) -> None:
+    """y = o' * rsqrt(mean over each group of ``group`` values of o'^2 + eps) * w * act(gate), o' = in_scale * o,
+    act the sigmoid or ("silu") the gate times its sigmoid;
     o float32 [T, n] contiguous, gate float32 rows [T, n] (a column section is fine), w float32 [n]."""
     T, n = o.shape
     if o.dtype != torch.float32 or not o.is_contiguous() or tuple(y.shape) != (T, n) or not y.is_contiguous():
@@ -924,7 +934,8 @@ def gated_group_norm(y, o, w, gate, group: int, eps: float) -> None:
         raise KernelError("gated_group_norm: weight [n] and gate [T, n]")
     gp, gts = _f32_rows(gate, "gate")
     _check(_lib().af_gated_group_norm(_ptr(y), c_int(dtype_code(y.dtype)), _ptr(o), _ptr(w, "w", torch.float32), gp, gts,
-                                      c_int(T), c_int(n), c_int(group), c_float(eps), _stream()))
+                                      c_int(T), c_int(n), c_int(group), c_float(eps), c_int(GATE_ACTS[gate_act]),
+                                      c_float(in_scale), _stream()))
 
 
 def gated_scan(y, proj, off_z: int, off_x: int, off_g: int, bz, bx, state, batch) -> None:
@@ -1314,10 +1325,14 @@ def expert_tc_tile(n_pairs: int, n_experts: int) -> int:
     return next((t for t in EXPERT_TC_TILES if t >= share), EXPERT_TC_TILES[-1])
 
 
-def expert_route(ids, wts, shared_gate, h, router, n_experts: int) -> None:
+def expert_route(ids, wts, shared_gate, h, router, n_experts: int, correction=None, groups: int = 1, keep: int = 1,
+                 normalise: bool = False, out_scale: float = 1.0) -> None:
     """Per row of h [T, H]: scores = sigmoid(router[:n_experts] h) in 32 bits; ids, wts [T, top] = the experts
     with the largest scores (equal scores: the lower index) and their scores; ``shared_gate`` float32 [T], when
-    given, = sigmoid(router[n_experts] h)."""
+    given, = sigmoid(router[n_experts] h).  ``correction`` (float32 [experts]) is added to the scores for the
+    choice only.  ``groups`` > 1: the experts form so many equal groups of neighbours, a group's score is the sum
+    of its two largest choice scores, and only experts of the ``keep`` best groups can be chosen.  ``normalise``:
+    the chosen scores are divided by their sum + 1e-20; ``out_scale`` multiplies the weights."""
     T, H = h.shape
     top = ids.shape[1]
     rows = n_experts + (1 if shared_gate is not None else 0)
@@ -1326,11 +1341,15 @@ def expert_route(ids, wts, shared_gate, h, router, n_experts: int) -> None:
     if tuple(ids.shape) != (T, top) or tuple(wts.shape) != (T, top) or not (ids.is_contiguous() and wts.is_contiguous()
                                                                            and h.is_contiguous()):
         raise KernelError("expert_route: ids and wts contiguous [T, top], h contiguous")
+    if correction is not None and (correction.numel() != n_experts or not correction.is_contiguous()):
+        raise KernelError(f"expert_route: a correction of {n_experts} values")
     scores = torch.empty(T, rows, dtype=torch.float32, device=h.device)      # (between the two kernels)
     _check(_lib().af_expert_route(_ptr(ids, "ids", torch.int32), _ptr(wts, "wts", torch.float32),
                                   _ptr(shared_gate, "shared_gate", torch.float32, allow_none=True), _ptr(scores), _ptr(h),
                                   c_int(dtype_code(h.dtype)), _ptr(router), c_int(T), c_int(H), c_int(n_experts),
-                                  c_int(top), _stream()))
+                                  c_int(top), _ptr(correction, "correction", torch.float32, allow_none=True),
+                                  c_int(groups), c_int(keep if groups > 1 else 1), c_int(1 if normalise else 0),
+                                  c_float(out_scale), _stream()))
 
 
 def expert_plan(perm, plan, ids, n_experts: int, tile: int = EXPERT_TILE) -> None:
@@ -1346,20 +1365,26 @@ def expert_plan(perm, plan, ids, n_experts: int, tile: int = EXPERT_TILE) -> Non
                                  c_int(tile), _stream()))
 
 
+EXPERT_ACTS = {None: 0, "gelu_erf": 1}
+
+
 def expert_rows(out, a, w0, w1=None, perm=None, plan=None, pair_weight=None, scale_out=None, n_tokens: int = 0,
-                top: int = 1, limit: float = 0.0) -> None:
+                top: int = 1, limit: float = 0.0, act=None) -> None:
     """Rows times the matrices of the expert they belong to (the CUDA-core path; 32-bit sums in index order).
     With ``w1``: out[sorted row] = act(s x w0[e]^T, s x w1[e]^T) * post in the compute dtype, x = row
     pair // top of ``a``, s = pair_weight[pair], post = scale_out[token], act(g, u) = min(g, limit)
     sigmoid(1.702 min(g, limit)) (clamp(u, +-limit) + 1).  Without: out float32 [top, tokens, N] with
-    out[choice, token] = a[sorted row] w0[e]^T.  w0, w1: [experts, N, K].  Without a plan: one expert, the
-    rows in order."""
+    out[choice, token] = a[sorted row] w0[e]^T.  Without ``w1`` but with ``act`` = "gelu_erf": an expert of one
+    matrix, out[sorted row] = gelu(x w0[e]^T) * s * post with the exact GELU (the weight stands behind the
+    activation).  w0, w1: [experts, N, K].  Without a plan: one expert, the rows in order."""
     n_rows = n_tokens * top
     E, N, K = w0.shape
     if not (a.is_contiguous() and out.is_contiguous() and w0.is_contiguous()) or a.shape[1] != K or a.dtype != w0.dtype:
         raise KernelError("expert_rows: contiguous rows of the matrices' dtype and row size")
-    if w1 is not None:
-        if w1.shape != w0.shape or w1.dtype != w0.dtype or not w1.is_contiguous():
+    if act not in EXPERT_ACTS or (act is not None and w1 is not None):
+        raise KernelError(f"expert_rows: activation '{act}' (known: gelu_erf, behind one matrix)")
+    if w1 is not None or act is not None:
+        if w1 is not None and (w1.shape != w0.shape or w1.dtype != w0.dtype or not w1.is_contiguous()):
             raise KernelError("expert_rows: gate and up matrices alike")
         if tuple(out.shape) != (n_rows, N) or out.dtype != a.dtype or a.shape[0] != n_tokens:
             raise KernelError(f"expert_rows: out [{n_rows}, {N}] of the rows' dtype")
@@ -1374,7 +1399,7 @@ def expert_rows(out, a, w0, w1=None, perm=None, plan=None, pair_weight=None, sca
                                  _ptr(pair_weight, "pair_weight", torch.float32, allow_none=True),
                                  _ptr(scale_out, "scale_out", torch.float32, allow_none=True), c_int(n_rows),
                                  c_int(n_tokens), c_int(top), c_int(max_tiles), c_int(N), c_int(K), c_float(limit),
-                                 _stream()))
+                                 c_int(EXPERT_ACTS[act]), _stream()))
 
 
 def expert_gather(out, x, perm, top: int) -> None:
@@ -1395,7 +1420,7 @@ def expert_rows_tc_supported(a, w0) -> bool:
 
 
 def expert_rows_tc(out, a, w0, w1=None, perm=None, plan=None, pair_weight=None, scale_out=None, n_tokens: int = 0,
-                   top: int = 1, limit: float = 0.0, tile: int = 0) -> None:
+                   top: int = 1, limit: float = 0.0, tile: int = 0, act=None) -> None:
     """:func:`expert_rows` on the tcgen05 tensor cores (bfloat16 operands, 32-bit sums in TMEM), with one
     difference: ``a`` holds the sorted rows themselves also for the first product (:func:`expert_gather`).
     ``tile``: the row tile the plan was made for (without a plan: chosen here)."""
@@ -1403,8 +1428,10 @@ def expert_rows_tc(out, a, w0, w1=None, perm=None, plan=None, pair_weight=None, 
     E, N, K = w0.shape
     if not expert_rows_tc_supported(a, w0) or tuple(a.shape) != (n_rows, K) or not out.is_contiguous():
         raise KernelError("expert_rows_tc: contiguous bfloat16 rows [rows, K], K a multiple of 8, 16-byte aligned")
-    if w1 is not None:
-        if w1.shape != w0.shape or w1.dtype != w0.dtype or not w1.is_contiguous() or w1.data_ptr() % 16:
+    if act not in EXPERT_ACTS or (act is not None and w1 is not None):
+        raise KernelError(f"expert_rows_tc: activation '{act}' (known: gelu_erf, behind one matrix)")
+    if w1 is not None or act is not None:
+        if w1 is not None and (w1.shape != w0.shape or w1.dtype != w0.dtype or not w1.is_contiguous() or w1.data_ptr() % 16):
             raise KernelError("expert_rows_tc: gate and up matrices alike")
         if tuple(out.shape) != (n_rows, N) or out.dtype != torch.bfloat16:
             raise KernelError(f"expert_rows_tc: out bfloat16 [{n_rows}, {N}]")
@@ -1423,7 +1450,150 @@ def expert_rows_tc(out, a, w0, w1=None, perm=None, plan=None, pair_weight=None, 
                                     _ptr(pair_weight, "pair_weight", torch.float32, allow_none=True),
                                     _ptr(scale_out, "scale_out", torch.float32, allow_none=True), c_int(n_rows),
                                     c_int(n_tokens), c_int(top), c_int(max_tiles), c_int(tile), c_int(N), c_int(K),
-                                    c_float(limit), _ptr(error_word(a.device), "err", torch.int32), _stream()))
+                                    c_float(limit), c_int(EXPERT_ACTS[act]),
+                                    _ptr(error_word(a.device), "err", torch.int32), _stream()))
+
+
+# ---------------------------------------------------------------- a residual stream in several copies
+
+HC_MAX_STREAMS = 8
+
+
+def _hc_stream(x, S: int, W: int, who: str):
+    if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != S * W or not x.is_contiguous():
+        raise KernelError(f"{who}: the streams are contiguous float32 [tokens, {S} * {W}]")
+    if not 1 <= S <= HC_MAX_STREAMS:
+        raise KernelError(f"{who}: 1 to {HC_MAX_STREAMS} streams")
+
+
+def hc_read(y, x, in_w, w, eps: float, offset: float, S: int) -> None:
+    """y = norm(sum_s in_w[s] x[:, s]) * (offset + w): x float32 [T, S * W] (stream after stream), y [T, W]."""
+    T, W = y.shape
+    _hc_stream(x, S, W, "hc_read")
+    if in_w.numel() != S or w.numel() != W or not y.is_contiguous():
+        raise KernelError("hc_read: one factor a stream, a weight of the row's size")
+    _check(_lib().af_hc_read(_ptr(y), c_int(dtype_code(y.dtype)), _ptr(x), _ptr(in_w, "in_w", torch.float32),
+                             _ptr(w, "w", torch.float32), c_float(eps), c_float(offset), c_int(T), c_int(S), c_int(W),
+                             _stream()))
+
+
+def hc_write(x, terms, mix, out_w, S: int, scale=None, y=None, in_next=None, w_next=None, eps: float = 0.0,
+             offset: float = 0.0) -> None:
+    """Every stream from the old ones and a sublayer's result r = sum of the ``terms`` (as in
+    :func:`add_scaled_rmsnorm`; one or two), times the per-channel ``scale`` when given:
+    x[:, t] <- sum_s mix[s, t] x[:, s] + out_w[t] r.  With ``y``: also y = norm(sum_s in_next[s] x[:, s]) *
+    (offset + w_next) of the new streams.  x float32 [T, S * W]; mix float32 [S, S]."""
+    T = x.shape[0]
+    W = x.shape[1] // S
+    _hc_stream(x, S, W, "hc_write")
+    if not 1 <= len(terms) <= 2:
+        raise KernelError("hc_write: one or two terms")
+    if mix.numel() != S * S or out_w.numel() != S or not mix.is_contiguous() or (scale is not None and scale.numel() != W):
+        raise KernelError("hc_write: mix [S, S], out_w [S], scale [W]")
+    if y is not None and (tuple(y.shape) != (T, W) or not y.is_contiguous() or in_next is None or in_next.numel() != S
+                          or w_next is None or w_next.numel() != W):
+        raise KernelError("hc_write: the next read wants y [T, W], in_next [S] and w_next [W]")
+    a, sa = terms[0]
+    b, sb = terms[1] if len(terms) > 1 else (None, 0.0)
+    barg = _term_arg(b, T, W, "hc_write") if b is not None else (ctypes.c_void_p(0), c_int(F32), c_int(1))
+    _check(_lib().af_hc_write(
+        _ptr(x), *_term_arg(a, T, W, "hc_write"), c_float(sa), *barg, c_float(sb),
+        _ptr(scale, "scale", torch.float32, allow_none=True), _ptr(mix, "mix", torch.float32),
+        _ptr(out_w, "out_w", torch.float32), _ptr(in_next, "in_next", torch.float32, allow_none=True),
+        _ptr(w_next, "w_next", torch.float32, allow_none=True), c_float(eps), c_float(offset),
+        _ptr(y, "y", allow_none=True), c_int(dtype_code(y.dtype) if y is not None else F32), c_int(T), c_int(S), c_int(W),
+        _stream()))
+
+
+def stream_copy(x, e, S: int) -> None:
+    """x[:, s] = e for every stream s: e float32 [T, W], x float32 [T, S * W]."""
+    T, W = e.shape
+    _hc_stream(x, S, W, "stream_copy")
+    if e.dtype != torch.float32 or not e.is_contiguous() or x.shape[0] != T:
+        raise KernelError("stream_copy: e contiguous float32 [T, W]")
+    _check(_lib().af_stream_copy(_ptr(x), _ptr(e), c_int(T), c_int(S), c_int(W), _stream()))
+
+
+def stream_sum(out, x, S: int) -> None:
+    """out = sum_s x[:, s] (32-bit, in index order)."""
+    T, W = out.shape
+    _hc_stream(x, S, W, "stream_sum")
+    if out.dtype != torch.float32 or not out.is_contiguous() or x.shape[0] != T:
+        raise KernelError("stream_sum: out contiguous float32 [T, W]")
+    _check(_lib().af_stream_sum(_ptr(out), _ptr(x), c_int(T), c_int(S), c_int(W), _stream()))
+
+
+# ---------------------------------------------------------------- gated linear attention, differential attention
+
+def channel_decay(alpha, proj, off_low: int, w2t, bias, tau: float) -> None:
+    """alpha [T, n] float32 = sigmoid(bias + low w2t)^(1 / tau), ``low`` the ``rank`` columns of the packed float32
+    projection rows at ``off_low``, w2t float32 [rank, n]."""
+    T, n = alpha.shape
+    rank = w2t.shape[0]
+    if alpha.dtype != torch.float32 or not alpha.is_contiguous() or tuple(w2t.shape) != (rank, n) or not w2t.is_contiguous() \
+            or bias.numel() != n or off_low + rank > proj.shape[1] or proj.shape[0] != T:
+        raise KernelError("channel_decay: alpha float32 [T, n], w2t [rank, n], bias [n], the low-rank section inside the row")
+    pp, ld = _f32_rows(proj, "proj")
+    _check(_lib().af_channel_decay(_ptr(alpha), pp, ld, c_int(off_low), _ptr(w2t, "w2t", torch.float32),
+                                   _ptr(bias, "bias", torch.float32), c_int(rank), c_int(T), c_int(n), c_float(tau),
+                                   _stream()))
+
+
+def conv_pack(qkv, proj, batch, H: int, G: int, d: int, dv: int, pk: int, pv: int, bias=None, taps_w=None, history=None,
+              temp_coef: float = 0.0, temp_every: int = 0, kv=None) -> None:
+    """From float32 projection rows [q (H heads of two maps of d) | k (G heads of two maps) | v (G heads of dv)], plus
+    ``bias``: a causal convolution over time on every channel (``taps_w`` float32 [taps, channels], the last tap on
+    the token itself; inputs before the step come from ``history`` float32 [slots, taps - 1, channels], which is
+    left holding the sequence's last taps - 1 inputs), the query temperature 1 + temp_coef ln(floor((p + 1) /
+    temp_every) + 1), and the packing for the grouped attention kernels with every map a head of its own:
+    ``qkv`` [T, (2 H + 2 G) pk + 2 G pv] of the compute dtype = 2 H query heads (group by group, first map's heads
+    then second map's), 2 G key heads (group, map), 2 G value heads (a group's values twice); heads ``pk`` / ``pv``
+    elements apart, zeros behind their own.  With ``kv`` the k and v heads also go to each token's cache row."""
+    T = proj.shape[0]
+    C = H * 2 * d + G * 2 * d + G * dv
+    taps = 1 if taps_w is None else taps_w.shape[0]
+    if proj.shape[1] < C or tuple(qkv.shape) != (T, (2 * H + 2 * G) * pk + 2 * G * pv) or pk < d or pv < dv or H % G:
+        raise KernelError("conv_pack: shapes of the projection and the packed rows do not fit")
+    if taps_w is not None and (tuple(taps_w.shape) != (taps, C) or taps_w.dtype != torch.float32 or not taps_w.is_contiguous()):
+        raise KernelError(f"conv_pack: taps float32 [taps, {C}]")
+    if taps > 1 and (history is None or history.dtype != torch.float32 or tuple(history.shape[1:]) != (taps - 1, C)
+                     or not history.is_contiguous()):
+        raise KernelError(f"conv_pack: a history float32 [slots, {taps - 1}, {C}]")
+    if bias is not None and bias.numel() != C:
+        raise KernelError(f"conv_pack: a bias of {C} values")
+    kc = vc = pt = None
+    max_pages = ring = 0
+    if kv is not None:
+        kc, vc, pt, ring = kv.k, kv.v, kv.page_table, kv.ring_rows
+        if kc.dtype != qkv.dtype or tuple(kc.shape[1:]) != (2 * G, PAGE, pk) or vc is None \
+                or tuple(vc.shape[1:]) != (2 * G, PAGE, pv) or not kc.is_contiguous() or not vc.is_contiguous():
+            raise KernelError(f"conv_pack: cache pages must be [pages, {2 * G}, {PAGE}, {pk}] (values {pv}) of the rows' dtype")
+        max_pages = pt.shape[1]
+    pp, ld = _f32_rows(proj, "proj")
+    i32 = torch.int32
+    _check(_lib().af_conv_pack(
+        _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_longlong(_rows(qkv, "qkv")), pp, ld,
+        _ptr(bias, "bias", torch.float32, allow_none=True), _ptr(taps_w, "taps_w", torch.float32, allow_none=True),
+        _ptr(history if taps > 1 else None, "history", torch.float32, allow_none=True),
+        _ptr(batch.positions, "positions", i32), _ptr(batch.seq_of_token, "seq_of_token", i32),
+        _ptr(batch.slots, "slots", i32), _ptr(batch.len_after, "len_after", i32), _ptr(batch.seq_starts, "seq_starts", i32),
+        c_int(T), c_int(batch.n_seqs), c_int(taps), c_int(H), c_int(G), c_int(d), c_int(dv), c_int(pk), c_int(pv),
+        c_float(temp_coef), c_int(temp_every), _ptr(kc, allow_none=True), _ptr(vc, allow_none=True),
+        _ptr(pt, "page_table", i32, allow_none=True), c_int(max_pages), c_int(ring), _stream()))
+
+
+def diff_join(y, ctx, gate, H: int, G: int, dv: int, pv: int, lam: float, eps: float, post: float, ones: int = 0) -> None:
+    """Per token and head h: o = a1 - lam a2 with a1, a2 the outputs of the head's two maps in ``ctx`` [T, 2 H pv]
+    (ordered as :func:`conv_pack` orders the queries), o / sqrt(mean(o^2) + eps) * post * sigmoid(gate[t, h]),
+    into y [T, >= H dv + ones]: the heads side by side, then ``ones`` columns of 1, then zeros.  ``gate``: float32
+    rows [T, H dv] (a column section is fine) or None."""
+    T = ctx.shape[0]
+    if tuple(ctx.shape) != (T, 2 * H * pv) or y.shape[0] != T or y.shape[1] < H * dv + ones or y.dtype != ctx.dtype:
+        raise KernelError("diff_join: shapes or dtypes do not fit")
+    gp, gts = _f32_rows(gate, "gate") if gate is not None else (ctypes.c_void_p(0), c_longlong(0))
+    _check(_lib().af_diff_join(_ptr(y), c_longlong(_rows(y, "y")), _ptr(ctx), c_longlong(_rows(ctx, "ctx")),
+                               c_int(dtype_code(ctx.dtype)), gp, gts, c_int(T), c_int(H), c_int(G), c_int(dv), c_int(pv),
+                               c_float(lam), c_float(eps), c_float(post), c_int(ones), _stream()))
 
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -13,6 +13,15 @@ u' = clamp(u, -limit, limit).  A shared expert of the same form (own size and li
 may run for every token; it is added times sigmoid(w_sg . h).  Nothing is read back
 by the host: the pairs are sorted by expert on the device and the products walk
 tiles of one expert's pairs, so a decode step can be captured.
+
+Other designs' routers and experts are options of the same part.  The router may add
+a learned correction to the scores *for the choice only*, may choose among the
+experts of the best groups only (``groups`` equal groups of neighbours, a group's
+score the sum of its two largest choice scores, the ``keep`` best kept), and may
+divide the chosen scores by their sum and multiply them by a constant.  An expert
+may be of one matrix and an activation, E(h) = W_down gelu(W_up h) with the exact
+(erf) GELU (``expert`` = "gelu_erf"); its weight then multiplies the expert's
+*output* (it is applied behind the activation, in front of the linear down product).
 """
 from __future__ import annotations
 
@@ -90,8 +99,10 @@ class RoutedExperts(FeedForward):
     """Parameters: ``hidden_size``, ``intermediate_size``, ``num_experts``, ``top``, ``limit``,
     ``router_weight`` ([experts, hidden]) and ``expert_weights``: a pattern with ``{e}`` for the expert's number
     and ``{role}`` for gate / up / down; optional ``shared``: {``intermediate_size``, ``limit``,
-    ``gate_weight``, ``up_weight``, ``down_weight``, ``mix_weight`` ([1, hidden])}.  The result is a sum of
-    32-bit terms that the residual kernel takes."""
+    ``gate_weight``, ``up_weight``, ``down_weight``, ``mix_weight`` ([1, hidden])}.  Optional ``expert``:
+    "clamped_glu" (the default, with ``limit``) or "gelu_erf" (up and down only; the weight on the output; no
+    ``limit``).  Optional ``router``: {``correction_weight`` (tensor name, [experts]), ``groups``: {``count``,
+    ``keep``}, ``normalise`` (bool), ``scale``}.  The result is a sum of 32-bit terms that the residual kernel takes."""
     graph_safe = True
 
     def __init__(self, params, ctx):
@@ -100,7 +111,21 @@ class RoutedExperts(FeedForward):
         self.inter = int(self.param("intermediate_size"))
         self.n_experts = int(self.param("num_experts"))
         self.top = int(self.param("top"))
-        self.limit = float(self.param("limit"))
+        self.expert = self.params.get("expert", "clamped_glu")
+        if self.expert not in ("clamped_glu", "gelu_erf"):
+            raise ConfigError(f"routed_experts: unknown expert '{self.expert}' (known: clamped_glu, gelu_erf)")
+        self.gated = self.expert == "clamped_glu"
+        self.limit = float(self.param("limit")) if self.gated else 0.0
+        ro = self.params.get("router") or {}
+        self.correction_name = ro.get("correction_weight")
+        groups = ro.get("groups") or {}
+        self.groups, self.keep = int(groups.get("count", 1)), int(groups.get("keep", 1))
+        self.normalise = bool(ro.get("normalise", False))
+        self.route_scale = float(ro.get("scale", 1.0))
+        if self.groups < 1 or self.n_experts % self.groups or not 1 <= self.keep <= self.groups:
+            raise ConfigError(f"routed_experts: {self.n_experts} experts in {self.groups} groups of which {self.keep} are kept")
+        if self.keep * (self.n_experts // self.groups) < self.top:
+            raise ConfigError(f"routed_experts: the kept groups hold fewer than the {self.top} experts a token uses")
         if not 1 <= self.top <= self.n_experts:
             raise ConfigError(f"routed_experts: {self.top} of {self.n_experts} experts")
         self.router_name = self.param("router_weight")
@@ -118,9 +143,12 @@ class RoutedExperts(FeedForward):
     def weight_decls(self):
         h, f = self.hidden, self.inter
         decls = [WeightDecl(self.router_name, (self.n_experts, h))]
+        if self.correction_name:
+            decls.append(WeightDecl(self.correction_name, (self.n_experts,), "norm"))
         for e in range(self.n_experts):
-            decls += [WeightDecl(self._name(e, "gate"), (f, h)), WeightDecl(self._name(e, "up"), (f, h)),
-                      WeightDecl(self._name(e, "down"), (h, f))]
+            if self.gated:
+                decls.append(WeightDecl(self._name(e, "gate"), (f, h)))
+            decls += [WeightDecl(self._name(e, "up"), (f, h)), WeightDecl(self._name(e, "down"), (h, f))]
         if self.shared is not None:
             sf, sh = int(self.shared["intermediate_size"]), self.shared
             decls += [WeightDecl(sh["gate_weight"], (sf, h)), WeightDecl(sh["up_weight"], (sf, h)),
@@ -130,7 +158,10 @@ class RoutedExperts(FeedForward):
     def load(self, weights):
         dt = self.ctx.compute_dtype
         E = range(self.n_experts)
-        self.w_gate = torch.stack([weights[self._name(e, "gate")] for e in E]).to(dt).contiguous()
+        self.w_gate = (torch.stack([weights[self._name(e, "gate")] for e in E]).to(dt).contiguous()
+                       if self.gated else None)
+        self.correction = (weights[self.correction_name].to(torch.float32).contiguous()
+                           if self.correction_name else None)
         self.w_up = torch.stack([weights[self._name(e, "up")] for e in E]).to(dt).contiguous()
         self.w_down = torch.stack([weights[self._name(e, "down")] for e in E]).to(dt).contiguous()
         rows = [weights[self.router_name]]
@@ -148,13 +179,14 @@ class RoutedExperts(FeedForward):
     def decode_bytes(self, lens) -> int:
         # the experts whose matrices are read: the expected number under a router that chooses evenly
         used = self.n_experts * (1.0 - (1.0 - self.top / self.n_experts) ** len(lens))
-        total = int(3 * used * self.hidden * self.inter * self._el()) + 4 * self.router.numel()
+        mats = 3 if self.gated else 2
+        total = int(mats * used * self.hidden * self.inter * self._el()) + 4 * self.router.numel()
         if self.shared is not None:
             total += 3 * self.hidden * int(self.shared["intermediate_size"]) * self._el()
         return total
 
     def prefill_flops(self, lens) -> int:
-        per_token = 3 * self.hidden * self.inter * self.top + self.router.numel()
+        per_token = (3 if self.gated else 2) * self.hidden * self.inter * self.top + self.router.numel()
         if self.shared is not None:
             per_token += 3 * self.hidden * int(self.shared["intermediate_size"])
         return 2 * sum(lens) * per_token
@@ -164,10 +196,12 @@ class RoutedExperts(FeedForward):
         ids = torch.empty(T, top, dtype=torch.int32, device=dev)
         wts = torch.empty(T, top, dtype=torch.float32, device=dev)
         mix = torch.empty(T, dtype=torch.float32, device=dev) if self.shared is not None else None
-        kernels.expert_route(ids, wts, mix, x, self.router, self.n_experts)
+        kernels.expert_route(ids, wts, mix, x, self.router, self.n_experts, correction=self.correction,
+                             groups=self.groups, keep=self.keep, normalise=self.normalise, out_scale=self.route_scale)
         # bfloat16 with sizes the tensor-core products take: the rows in sorted order, then grouped products;
         # else the products on the CUDA cores (32-bit, or odd sizes), which fetch their rows themselves
-        fast = (kernels.expert_rows_tc_supported(x, self.w_gate) and self.inter % 8 == 0)
+        fast = (kernels.expert_rows_tc_supported(x, self.w_up) and self.inter % 8 == 0)
+        act = None if self.gated else "gelu_erf"
         tile = kernels.expert_tc_tile(T * top, self.n_experts) if fast else kernels.EXPERT_TILE
         perm = torch.empty(T * top, dtype=torch.int32, device=dev)
         plan = torch.empty(1 + 3 * kernels.expert_max_tiles(T * top, self.n_experts, tile), dtype=torch.int32, device=dev)
@@ -177,12 +211,19 @@ class RoutedExperts(FeedForward):
         if fast:
             rows = torch.empty(T * top, self.hidden, dtype=x.dtype, device=dev)
             kernels.expert_gather(rows, x, perm, top)
-            kernels.expert_rows_tc(mid, rows, self.w_gate, self.w_up, perm=perm, plan=plan, pair_weight=wts, n_tokens=T,
-                                   top=top, limit=self.limit, tile=tile)
+            if self.gated:
+                kernels.expert_rows_tc(mid, rows, self.w_gate, self.w_up, perm=perm, plan=plan, pair_weight=wts,
+                                       n_tokens=T, top=top, limit=self.limit, tile=tile)
+            else:
+                kernels.expert_rows_tc(mid, rows, self.w_up, perm=perm, plan=plan, pair_weight=wts, n_tokens=T, top=top,
+                                       tile=tile, act=act)
             kernels.expert_rows_tc(out, mid, self.w_down, perm=perm, plan=plan, n_tokens=T, top=top, tile=tile)
         else:
-            kernels.expert_rows(mid, x, self.w_gate, self.w_up, perm=perm, plan=plan, pair_weight=wts, n_tokens=T,
-                                top=top, limit=self.limit)
+            if self.gated:
+                kernels.expert_rows(mid, x, self.w_gate, self.w_up, perm=perm, plan=plan, pair_weight=wts, n_tokens=T,
+                                    top=top, limit=self.limit)
+            else:
+                kernels.expert_rows(mid, x, self.w_up, perm=perm, plan=plan, pair_weight=wts, n_tokens=T, top=top, act=act)
             kernels.expert_rows(out, mid, self.w_down, perm=perm, plan=plan, n_tokens=T, top=top)
         terms = [(PartialSums(out), 1.0)]
         if self.shared is not None:

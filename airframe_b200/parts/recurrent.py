@@ -321,3 +321,82 @@ class RgLru(_StateMixer):
         y = torch.empty(T, w, dtype=x.dtype, device=x.device)
         kernels.decay_scan(y, decay, inp, proj, off["y"], off["x"], self.y_bias, self.x_bias, view.state, batch)
         return linear_split(y, self.w_o, wide=self.wide)
+
+
+@register_part("mixer", "gated_linear_attention")
+class GatedLinearAttention(_StateMixer):
+    """Linear attention whose state decays by a factor per key channel and token:
+
+        q = query_scale W_q h, k = W_k h, v = W_v h, alpha = sigmoid(W_a2 (W_a1 h) + b_a2)^(1 / tau)
+        S <- diag(alpha) S + k v^T (per head, from zero), o = S^T q
+
+    each head's o is divided by its root mean square (``eps`` inside the root), times a weight of ``value_dim``
+    values that the heads share, times silu(W_g h), then the output projection.
+
+    Parameters: ``hidden_size``, ``num_heads``, ``head_dim`` (queries and keys), ``value_dim``, ``tau``, ``eps``,
+    ``weights``: tensor names for ``q, k, v, g, a1, a2, a2_bias, norm, o``; optional ``query_scale`` (default
+    head_dim^-1/2), ``decay_rank`` (rows of a1; read from the tensor when absent), ``gate`` ("silu", the default, or
+    "sigmoid")."""
+    ROLES = ("q", "k", "v", "g", "a1", "a2", "a2_bias", "norm", "o")
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(self.param("hidden_size"))
+        self.heads = int(self.param("num_heads"))
+        self.dk = int(self.param("head_dim"))
+        self.dv = int(self.param("value_dim"))
+        self.tau = float(self.param("tau"))
+        self.eps = float(self.param("eps"))
+        if not self.tau > 0:
+            raise ConfigError("gated_linear_attention: tau must be > 0")
+        self.query_scale = float(self.params.get("query_scale", self.dk ** -0.5))
+        rank = self.params.get("decay_rank")
+        self.rank = int(rank) if rank is not None else None
+        self.gate = self.params.get("gate", "silu")
+        if self.gate not in kernels.GATE_ACTS:
+            raise ConfigError(f"gated_linear_attention: unknown gate '{self.gate}' (known: {sorted(kernels.GATE_ACTS)})")
+        self.names = self._names(self.ROLES)
+
+    def state_need(self):
+        return StateNeed((self.heads, self.dv, self.dk), "float32")      # [head][value column][key channel]
+
+    def weight_decls(self):
+        nk, nv, h, nm = self.heads * self.dk, self.heads * self.dv, self.hidden, self.names
+        return [WeightDecl(nm["q"], (nk, h)), WeightDecl(nm["k"], (nk, h)), WeightDecl(nm["v"], (nv, h)),
+                WeightDecl(nm["g"], (nv, h)), WeightDecl(nm["a1"], (self.rank, h)), WeightDecl(nm["a2"], (nk, self.rank)),
+                WeightDecl(nm["a2_bias"], (nk,), "norm"), WeightDecl(nm["norm"], (self.dv,), "gain"),
+                WeightDecl(nm["o"], (h, nv))]
+
+    def load(self, weights):
+        nm, f32 = self.names, torch.float32
+        self.rank = weights[nm["a1"]].shape[0]
+        if weights[nm["a2"]].shape[1] != self.rank:
+            raise ConfigError(f"gated_linear_attention: {nm['a1']} has {self.rank} rows, {nm['a2']} has "
+                              f"{weights[nm['a2']].shape[1]} columns")
+        self.w_in, self.off = self._pack(weights, ("q", "k", "v", "g", "a1"))
+        self.w2t = weights[nm["a2"]].to(f32).t().contiguous()            # [rank, heads * dim]: channels side by side
+        self.a2_bias = weights[nm["a2_bias"]].to(f32).contiguous()
+        self.norm_w = weights[nm["norm"]].to(f32).repeat(self.heads).contiguous()      # the heads share it
+        self.w_o = weights[nm["o"]].to(self.ctx.compute_dtype).contiguous()
+
+    def decode_bytes(self, lens) -> int:
+        weights = (self.w_in.numel() + self.w_o.numel()) * _el(self.ctx) + 4 * self.w2t.numel()
+        return weights + len(lens) * 2 * 4 * self.heads * self.dk * self.dv      # the state, read and written
+
+    def prefill_flops(self, lens) -> int:
+        T = sum(lens)
+        return 2 * T * (self.w_in.numel() + self.w_o.numel() + self.w2t.numel()) + T * self.heads * 5 * self.dk * self.dv
+
+    def forward(self, x, batch, view):
+        T, off, f32 = x.shape[0], self.off, torch.float32
+        nk, nv = self.heads * self.dk, self.heads * self.dv
+        proj = linear(x, self.w_in, out_dtype=f32)
+        alpha = torch.empty(T, nk, dtype=f32, device=x.device)
+        kernels.channel_decay(alpha, proj, off["a1"], self.w2t, self.a2_bias, self.tau)
+        o = torch.empty(T, nv, dtype=f32, device=x.device)
+        kernels.state_scan("channel", o, proj[:, off["q"]: off["q"] + nk], proj[:, off["k"]: off["k"] + nk],
+                           proj[:, off["v"]: off["v"] + nv], view.state, batch, self.heads, self.dk, self.dv, w=alpha)
+        y = torch.empty(T, nv, dtype=x.dtype, device=x.device)
+        kernels.gated_group_norm(y, o, self.norm_w, proj[:, off["g"]: off["g"] + nv], self.dv, self.eps,
+                                 gate_act=self.gate, in_scale=self.query_scale)
+        return linear_split(y, self.w_o, wide=self.wide)

@@ -25,7 +25,7 @@ from .safetensors_io import SafetensorsError, SafetensorsFile
 @dataclass
 class WeightDecl:
     """A tensor that a part needs.  ``kind`` tells the random-weights mode how
-    to fill it: ``matrix`` and ``table`` N(0, 0.02), ``norm`` N(0, 0.1), ``gain`` N(1, 0.1),
+    to fill it: ``matrix`` and ``table`` N(0, 0.02), ``norm`` N(0, 0.1), ``gain`` N(1, 0.1), ``mixing`` identity + N(0, 0.1), ``share`` N(1, 0.1) / n,
     ``int_table`` integers.  A ``None`` in ``shape`` stands for a size that only
     the stored tensor gives (the part reads it when it loads)."""
     name: str

@@ -1,7 +1,8 @@
 """Seeded random weights: a source that makes each declared tensor from
 (seed, tensor name), and a writer of whole model folders (config.json and
 model.safetensors).  Matrices and tables are N(0, 0.02), norm weights
-N(0, 0.1) (they act as ``offset + w``), gains (factors used as they stand) N(1, 0.1).
+N(0, 0.1) (they act as ``offset + w``), gains (factors used as they stand) N(1, 0.1),
+mixing matrices the identity + N(0, 0.1), shares (the n factors of a weighted mean) N(1, 0.1) / n.
 
 The reference has no such mode (its tests use zeros and ones,
 ``src/family/llama.rs:625-682``).
@@ -17,7 +18,7 @@ import torch
 from .loader import WeightDecl
 from .safetensors_io import write_safetensors
 
-_STD = {"matrix": 0.02, "table": 0.02, "norm": 0.1, "gain": 0.1}
+_STD = {"matrix": 0.02, "table": 0.02, "norm": 0.1, "gain": 0.1, "mixing": 0.1, "share": 0.1}
 _MEAN = {"gain": 1.0}      # a factor that is used as it stands (a norm weight that acts as ``offset + w`` is "norm")
 _STORE = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}
 
@@ -43,6 +44,10 @@ def random_tensor(decl: WeightDecl, seed: int, dtype: torch.dtype, device="cpu")
     t.normal_(0.0, _STD[decl.kind], generator=gen)
     if decl.kind in _MEAN:
         t += _MEAN[decl.kind]
+    if decl.kind == "mixing":            # a square matrix that mixes copies of a stream: near the identity
+        t += torch.eye(decl.shape[0], dtype=torch.float32, device=device)
+    if decl.kind == "share":             # factors of a weighted mean: near 1 / n
+        t = (t + 1.0) / decl.shape[0]
     return t.to(dtype)
 
 
