@@ -33,7 +33,7 @@ def main(argv=None) -> int:
     ap.add_argument("--model", default=os.environ.get("LIBSHIMMY_MODEL_PATH"),
                     help="model folder (config.json, model.safetensors); default $LIBSHIMMY_MODEL_PATH")
     ap.add_argument("--random", metavar="NAME", default=None,
-                    help="no folder: seeded random weights of a named configuration (tinyA, tinyB, 2b, 9b, 27b, fiferax-small, banitar-small, zatasun-small)")
+                    help="no folder: seeded random weights of a named configuration (tinyA, tinyB, 2b, 9b, 27b, fiferax-small, banitar-small, zatasun-small, tarorax-small)")
     ap.add_argument("--prompt-ids", action="append", default=[], metavar="IDS",
                     help="token ids of one request (as the positional prompts); may be repeated")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])

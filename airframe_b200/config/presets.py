@@ -1,5 +1,5 @@
 """Named configurations for the random-weights mode: the two tiny test
-models, the layer sizes of the released Gemma-2 models, a small Fiferax, a small Banitar and a small Zatasun, as
+models, the layer sizes of the released Gemma-2 models, a small Fiferax, a small Banitar, a small Zatasun and a small Tarorax, as
 config.json dictionaries.  Nothing here is read by the model code: a configuration always
 reaches it through ``config_from_dict``."""
 from __future__ import annotations
@@ -83,6 +83,22 @@ def _zatasun_small() -> dict:
 
 
 PRESETS["zatasun-small"] = _zatasun_small()
+
+
+def _tarorax_small() -> dict:
+    """Tarorax with four layers over four streams, the third of them differential attention; dense and routed
+    feed-forwards in turn (sizes of no released model)."""
+    gla = {"heads": 8, "dim": 64, "vdim": 64, "tau": 16.0, "rank": 32}
+    att = {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 128, "conv": 4, "diff": 0.6, "scale": 0.125, "softcap": 50.0,
+           "q_temp": {"coef": 0.5, "every": 64}}
+    moe = {"kind": "moe", "expert": {"ff": 256}, "router": {"experts": 8, "top": 2, "scale": 2.0,
+                                                            "groups": {"count": 4, "keep": 2}}}
+    layers = [{"type": "attention" if i == 2 else "gla", "mixer": att if i == 2 else gla,
+               "mlp": {"kind": "dense", "ff": 1536} if i % 2 == 0 else moe} for i in range(4)]
+    return {"architecture": "Tarorax", "vocab": 8192, "width": 512, "norm": {"eps": 1e-6}, "streams": 4, "layers": layers}
+
+
+PRESETS["tarorax-small"] = _tarorax_small()
 
 
 def preset(name: str) -> dict:

@@ -44,73 +44,168 @@ __device__ __forceinline__ float conv_input(const AfConvArgs& a, int t, int pos,
   return a.history[((size_t)slot * (a.taps - 1) + (a.taps - 1 - k)) * C + c];
 }
 
-template <typename T>
+// VEC packed elements a thread (neighbours within one head; VEC divides every head's sizes and pitches): block (x, y)
+// takes elements 256 VEC y .. of token x's packed row (the q heads, then the k heads, then the v heads, padding
+// included).  Where an element comes from and where it goes is worked out once for the VEC of them.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 conv_pack_kernel(T* __restrict__ qkv, long long out_stride, AfConvArgs a, T* __restrict__ kcache, T* __restrict__ vcache) {
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int cq = a.H * 2 * a.d, ck = a.G * 2 * a.d, cv = a.G * a.dv, C = cq + ck + cv;
   const int rep = a.H / a.G;
+  const int nq = 2 * a.H, nk = 2 * a.G;
+  const int n_q = nq * a.pk, n_k = nk * a.pk, n_v = nk * a.pv;
+  const int i = (blockIdx.y * 256 + threadIdx.x) * VEC;
+  if (i >= n_q + n_k + n_v) return;
+  // the channel of the projection that the first element is made from (-1: padding), and where it goes in a cache row
+  int c = -1, head = 0, e = 0, kind = 0;            // kind 0: q, 1: k, 2: v
+  if (i < n_q) {
+    head = i / a.pk, e = i - head * a.pk;
+    const int g = head / (2 * rep), m = (head / rep) & 1, j = head % rep;
+    if (e < a.d) c = ((g * rep + j) * 2 + m) * a.d + e;
+  } else if (i < n_q + n_k) {
+    const int x = i - n_q;
+    head = x / a.pk, e = x - head * a.pk, kind = 1;
+    if (e < a.d) c = cq + head * a.d + e;           // (head = 2 g + m, as the projection lays them out)
+  } else {
+    const int x = i - n_q - n_k;
+    head = x / a.pv, e = x - head * a.pv, kind = 2;
+    if (e < a.dv) c = cq + ck + (head >> 1) * a.dv + e;
+  }
+  const int taps = a.taps;
+  float w[8][VEC], bias[VEC];
+#pragma unroll
+  for (int x = 0; x < VEC; ++x) bias[x] = (c >= 0 && a.bias != nullptr) ? a.bias[c + x] : 0.f;
+  if (c >= 0 && a.taps_w != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int x = 0; x < VEC; ++x) w[j][x] = j < taps ? a.taps_w[(size_t)j * C + c + x] : 0.f;
+  }
   const int pos = a.positions[t];
   const int seq = a.seq_of_token[t];
   const int slot = a.slots[seq];
-  const int first_row = a.seq_starts[seq];
-  const int first_pos = pos - (t - first_row);
-  float temp = 1.f;
-  if (a.temp_every > 0) temp = 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every + 1));
-  // where this token's k and v rows go in the cache
-  T *kdst = nullptr, *vdst = nullptr;
-  if (kcache != nullptr && slot >= 0 && !(a.ring_rows > 0 && pos + a.ring_rows < a.len_after[seq])) {
+  const int first_pos = pos - (t - a.seq_starts[seq]);
+  T* cache = nullptr;
+  if (kind != 0 && kcache != nullptr && slot >= 0 && !(a.ring_rows > 0 && pos + a.ring_rows < a.len_after[seq])) {
     const int r = a.ring_rows > 0 ? pos % a.ring_rows : pos;
     if (AF_INDEX_OK(pos >= 0 && r / AF_PAGE < a.max_pages, r)) {
       const int page = a.page_table[(size_t)slot * a.max_pages + r / AF_PAGE];
       if (AF_INDEX_OK(page >= 0, page)) {
-        const size_t at = (size_t)page * (2 * a.G) * AF_PAGE + r % AF_PAGE;      // head 0's row; heads AF_PAGE rows apart
-        kdst = kcache + at * a.pk;
-        vdst = vcache + at * a.pv;
+        const size_t at = ((size_t)page * nk + head) * AF_PAGE + r % AF_PAGE;
+        cache = kind == 1 ? kcache + at * a.pk + e : vcache + at * a.pv + e;
       }
     }
   }
   pdl_wait();
   a.proj = pdl_fresh(a.proj);
-  T* row = qkv + (size_t)t * out_stride;
-  const int nq = 2 * a.H, nk = 2 * a.G;
-  // one packed element a thread and turn: the q heads, then the k heads, then the v heads, padding included
-  const int n_q = nq * a.pk, n_k = nk * a.pk, n_v = nk * a.pv;
-  for (int i = threadIdx.x; i < n_q + n_k + n_v; i += blockDim.x) {
-    int c = -1;                 // the channel of the projection that this element is made from (-1: padding)
-    float factor = 1.f;
-    T* cache = nullptr;
-    if (i < n_q) {
-      const int head = i / a.pk, e = i - head * a.pk;
-      const int g = head / (2 * rep), m = (head / rep) & 1, j = head % rep;
-      if (e < a.d) c = ((g * rep + j) * 2 + m) * a.d + e, factor = temp;
-    } else if (i < n_q + n_k) {
-      const int x = i - n_q, head = x / a.pk, e = x - head * a.pk;
-      if (e < a.d) c = cq + head * a.d + e;                      // (head = 2 g + m, as the projection lays them out)
-      if (kdst != nullptr) cache = kdst + (size_t)head * AF_PAGE * a.pk + e;
+  float v[VEC];
+#pragma unroll
+  for (int x = 0; x < VEC; ++x) v[x] = 0.f;
+  if (c >= 0) {
+    if (a.taps_w == nullptr) {
+#pragma unroll
+      for (int x = 0; x < VEC; ++x) v[x] = a.proj[(size_t)t * a.ld + c + x] + bias[x];
     } else {
-      const int x = i - n_q - n_k, head = x / a.pv, e = x - head * a.pv;
-      if (e < a.dv) c = cq + ck + (head >> 1) * a.dv + e;
-      if (vdst != nullptr) cache = vdst + (size_t)head * AF_PAGE * a.pv + e;
-    }
-    float v = 0.f;
-    if (c >= 0) {
-      if (a.taps_w == nullptr) {
-        v = conv_input(a, t, pos, pos, first_row, first_pos, slot, C, c);
-      } else {
-        for (int j = 0; j < a.taps; ++j) {
-          const int p = pos - (a.taps - 1) + j;
-          if (p < 0 || (p < first_pos && slot < 0)) continue;
-          v = fmaf(a.taps_w[(size_t)j * C + c], conv_input(a, t, pos, p, first_row, first_pos, slot, C, c), v);
+      // the inputs of all taps first (they do not depend on one another), then the sums in tap order
+      float u[8][VEC];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int x = 0; x < VEC; ++x) u[j][x] = 0.f;
+        if (j >= taps) continue;
+        const int p = pos - (taps - 1) + j;
+        if (p < 0) continue;
+        if (p >= first_pos) {
+          const float* src = a.proj + (size_t)(t - (pos - p)) * a.ld + c;
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) u[j][x] = src[x] + bias[x];
+        } else if (slot >= 0) {
+          const float* src = a.history + ((size_t)slot * (taps - 1) + (taps - 1 - (first_pos - p))) * C + c;
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) u[j][x] = src[x];
         }
       }
-      v *= factor;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < taps) {
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) v[x] = fmaf(w[j][x], u[j][x], v[x]);
+        }
     }
-    const T out = from_f32<T>(v);
-    row[i] = out;
-    if (cache != nullptr) *cache = out;
+    if (kind == 0 && a.temp_every > 0) {
+      const float temp = 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every + 1));
+#pragma unroll
+      for (int x = 0; x < VEC; ++x) v[x] *= temp;
+    }
   }
+  T* dst = qkv + (size_t)t * out_stride + i;
+#pragma unroll
+  for (int x = 0; x < VEC; ++x) {
+    const T out = from_f32<T>(v[x]);
+    dst[x] = out;
+    if (cache != nullptr) cache[x] = out;
+  }
+}
+
+// The same for more than eight taps: a loop over the taps, nothing held in registers.
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_pack_long_kernel(T* __restrict__ qkv, long long out_stride, AfConvArgs a, T* __restrict__ kcache,
+                      T* __restrict__ vcache) {
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int cq = a.H * 2 * a.d, ck = a.G * 2 * a.d, cv = a.G * a.dv, C = cq + ck + cv;
+  const int rep = a.H / a.G;
+  const int nq = 2 * a.H, nk = 2 * a.G;
+  const int n_q = nq * a.pk, n_k = nk * a.pk, n_v = nk * a.pv;
+  const int i = blockIdx.y * 256 + threadIdx.x;
+  if (i >= n_q + n_k + n_v) return;
+  int c = -1, head = 0, e = 0, kind = 0;
+  if (i < n_q) {
+    head = i / a.pk, e = i - head * a.pk;
+    const int g = head / (2 * rep), m = (head / rep) & 1, j = head % rep;
+    if (e < a.d) c = ((g * rep + j) * 2 + m) * a.d + e;
+  } else if (i < n_q + n_k) {
+    const int x = i - n_q;
+    head = x / a.pk, e = x - head * a.pk, kind = 1;
+    if (e < a.d) c = cq + head * a.d + e;
+  } else {
+    const int x = i - n_q - n_k;
+    head = x / a.pv, e = x - head * a.pv, kind = 2;
+    if (e < a.dv) c = cq + ck + (head >> 1) * a.dv + e;
+  }
+  const int pos = a.positions[t];
+  const int seq = a.seq_of_token[t];
+  const int slot = a.slots[seq];
+  const int first_row = a.seq_starts[seq];
+  const int first_pos = pos - (t - first_row);
+  T* cache = nullptr;
+  if (kind != 0 && kcache != nullptr && slot >= 0 && !(a.ring_rows > 0 && pos + a.ring_rows < a.len_after[seq])) {
+    const int r = a.ring_rows > 0 ? pos % a.ring_rows : pos;
+    if (AF_INDEX_OK(pos >= 0 && r / AF_PAGE < a.max_pages, r)) {
+      const int page = a.page_table[(size_t)slot * a.max_pages + r / AF_PAGE];
+      if (AF_INDEX_OK(page >= 0, page)) {
+        const size_t at = ((size_t)page * nk + head) * AF_PAGE + r % AF_PAGE;
+        cache = kind == 1 ? kcache + at * a.pk + e : vcache + at * a.pv + e;
+      }
+    }
+  }
+  pdl_wait();
+  a.proj = pdl_fresh(a.proj);
+  float v = 0.f;
+  if (c >= 0) {
+    for (int j = 0; j < a.taps; ++j) {
+      const int p = pos - (a.taps - 1) + j;
+      if (p < 0 || (p < first_pos && slot < 0)) continue;
+      v = fmaf(a.taps_w[(size_t)j * C + c], conv_input(a, t, pos, p, first_row, first_pos, slot, C, c), v);
+    }
+    if (kind == 0 && a.temp_every > 0) v *= 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every + 1));
+  }
+  const T out = from_f32<T>(v);
+  qkv[(size_t)t * out_stride + i] = out;
+  if (cache != nullptr) *cache = out;
 }
 
 // One thread a (sequence, channel): the history after the step = the last taps - 1 of (history, the step's values).
@@ -147,8 +242,20 @@ AF_EXPORT int af_conv_pack(void* qkv, int dtype, long long out_stride, const flo
   AF_REQUIRE((kcache == nullptr) == (vcache == nullptr), "af_conv_pack: key and value pages, or neither");
   AfConvArgs a{proj, ld, bias, taps_w, history, positions, seq_of_token, slots, len_after, seq_starts, taps, H, G, d, dv,
                pk, pv, temp_coef, temp_every, page_table, max_pages, ring_rows};
-  AF_DISPATCH_DTYPE(dtype, T, af_launch(conv_pack_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (T*)qkv, out_stride, a,
-                                        (T*)kcache, (T*)vcache));
+  const int n_el = (2 * H + 2 * G) * pk + 2 * G * pv;
+  const dim3 grid(n_tokens, (n_el + 255) / 256);
+  AF_REQUIRE(grid.y < 65536, "af_conv_pack: rows of %d elements are too long for one grid", n_el);
+  if (taps <= 8 && d % 4 == 0 && dv % 4 == 0 && pk % 4 == 0 && pv % 4 == 0) {
+    const dim3 grid4(n_tokens, (n_el / 4 + 255) / 256);
+    AF_DISPATCH_DTYPE(dtype, T, af_launch(conv_pack_kernel<T, 4>, grid4, dim3(256), 0, stream, (T*)qkv, out_stride, a,
+                                          (T*)kcache, (T*)vcache));
+  } else if (taps <= 8) {
+    AF_DISPATCH_DTYPE(dtype, T, af_launch(conv_pack_kernel<T, 1>, grid, dim3(256), 0, stream, (T*)qkv, out_stride, a,
+                                          (T*)kcache, (T*)vcache));
+  } else {
+    AF_DISPATCH_DTYPE(dtype, T, af_launch(conv_pack_long_kernel<T>, grid, dim3(256), 0, stream, (T*)qkv, out_stride, a,
+                                          (T*)kcache, (T*)vcache));
+  }
   AF_COUNT_LAUNCH("af_conv_pack");
   if (taps > 1) {
     const int C = H * 2 * d + G * 2 * d + G * dv;

@@ -68,7 +68,7 @@ __device__ __forceinline__ void hc_store(float* p, const float* v) {
 
 // y[t] = norm(sum_s in[s] x[t][s]) (offset + w)
 template <typename TY, int VEC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(640)
 hc_read_kernel(TY* __restrict__ y, const float* __restrict__ x, const float* __restrict__ in_w,
                const float* __restrict__ w, float eps, float offset, int S, int W) {
   pdl_launch_dependents();
@@ -105,7 +105,7 @@ hc_read_kernel(TY* __restrict__ y, const float* __restrict__ x, const float* __r
 
 // x[t][.] rewritten from the sublayer's result; with y: the next sublayer's norm(sum_s in_next[s] x'[t][s]) (offset + w_next)
 template <typename TY, int VEC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(640)
 hc_write_kernel(float* __restrict__ x, AfHcTerm a, AfHcTerm b, size_t part_stride, const float* __restrict__ ls,
                 const float* __restrict__ mix, const float* __restrict__ out_w, const float* __restrict__ in_next,
                 const float* __restrict__ w_next, float eps, float offset, TY* __restrict__ y, int S, int W) {
@@ -113,7 +113,7 @@ hc_write_kernel(float* __restrict__ x, AfHcTerm a, AfHcTerm b, size_t part_strid
   extern __shared__ float row[];
   __shared__ float scratch[33];
   __shared__ float cmix[AF_HC_MAX * AF_HC_MAX], cout[AF_HC_MAX], cin[AF_HC_MAX];
-  if (threadIdx.x < S * S) cmix[threadIdx.x] = mix[threadIdx.x];
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) cmix[i] = mix[i];      // (a block may have fewer threads than S * S)
   if (threadIdx.x < S) {
     cout[threadIdx.x] = out_w[threadIdx.x];
     cin[threadIdx.x] = in_next != nullptr ? in_next[threadIdx.x] : 0.f;
@@ -202,9 +202,14 @@ stream_sum_kernel(float* __restrict__ out, const float* __restrict__ x, int S, i
   }
 }
 
-static int hc_threads(int W, int vec) {
-  int th = ((W / vec + 31) / 32) * 32;
-  return th < 32 ? 32 : th > 256 ? 256 : th;
+// Threads of a token's block: as many as give every thread the same number of channel groups, up to 640 (a row of
+// up to 2560 values is then one group of four a thread, all its loads in flight at once).
+static int hc_threads(int W, int vec, int n_tokens) {
+  (void)n_tokens;
+  const int groups = (W + vec - 1) / vec;
+  const int iters = (groups + 639) / 640;
+  int th = (((groups + iters - 1) / iters + 31) / 32) * 32;
+  return th < 32 ? 32 : th > 640 ? 640 : th;
 }
 
 AF_EXPORT int af_hc_read(void* y, int y_dtype, const float* x, const float* in_w, const float* w, float eps, float offset,
@@ -215,10 +220,10 @@ AF_EXPORT int af_hc_read(void* y, int y_dtype, const float* x, const float* in_w
   const bool vec = W % 4 == 0 && ((uintptr_t)x & 15) == 0;
   const size_t smem = (size_t)W * sizeof(float);
   if (vec) {
-    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_read_kernel<TY, 4>, dim3(n_tokens), dim3(hc_threads(W, 4)), smem, stream,
+    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_read_kernel<TY, 4>, dim3(n_tokens), dim3(hc_threads(W, 4, n_tokens)), smem, stream,
                                              (TY*)y, x, in_w, w, eps, offset, S, W));
   } else {
-    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_read_kernel<TY, 1>, dim3(n_tokens), dim3(hc_threads(W, 1)), smem, stream,
+    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_read_kernel<TY, 1>, dim3(n_tokens), dim3(hc_threads(W, 1, n_tokens)), smem, stream,
                                              (TY*)y, x, in_w, w, eps, offset, S, W));
   }
   AF_CHECK_LAUNCH("af_hc_read");
@@ -243,10 +248,10 @@ AF_EXPORT int af_hc_write(float* x, const void* a, int a_dtype, int a_parts, flo
   const bool vec = W % 4 == 0 && (((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)ls) & 15) == 0;
   const size_t smem = y != nullptr ? (size_t)W * sizeof(float) : 0;
   if (vec) {
-    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_write_kernel<TY, 4>, dim3(n_tokens), dim3(hc_threads(W, 4)), smem, stream, x,
+    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_write_kernel<TY, 4>, dim3(n_tokens), dim3(hc_threads(W, 4, n_tokens)), smem, stream, x,
                                              ta, tb, part_stride, ls, mix, out_w, in_next, w_next, eps, offset, (TY*)y, S, W));
   } else {
-    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_write_kernel<TY, 1>, dim3(n_tokens), dim3(hc_threads(W, 1)), smem, stream, x,
+    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_write_kernel<TY, 1>, dim3(n_tokens), dim3(hc_threads(W, 1, n_tokens)), smem, stream, x,
                                              ta, tb, part_stride, ls, mix, out_w, in_next, w_next, eps, offset, (TY*)y, S, W));
   }
   AF_CHECK_LAUNCH("af_hc_write");

@@ -717,32 +717,64 @@ AF_EXPORT int af_gated_scan(void* y, int y_dtype, const float* proj, long long l
 // float32 projection rows that begin at off_low (the first factor of a low-rank pair, applied with the other
 // projections), w2t [rank, n] the second factor transposed.  Worked out as exp(log(sigmoid(z)) / tau) with
 // log(sigmoid(z)) = min(z, 0) - log1p(exp(-|z|)): 32-bit throughout, no underflow of the sigmoid on the way.
-// One block per token; the token's low-rank row lies in shared memory.
-__global__ void __launch_bounds__(256)
+// A block owns AF_CD_TOK tokens and a thread a channel (128 a block; 32 while the step is small, so that more
+// blocks stream the matrix): the tokens' low-rank rows lie in shared memory, a value of w2t is read once for all of
+// the block's tokens (eight of them asked for ahead), and a token's sum runs over r in index order whatever else is
+// in the step.
+#define AF_CD_TOK 16
+__global__ void __launch_bounds__(128)
 channel_decay_kernel(float* __restrict__ alpha, const float* __restrict__ proj, long long ld, int off_low,
-                     const float* __restrict__ w2t, const float* __restrict__ bias, int rank, int n, float inv_tau) {
+                     const float* __restrict__ w2t, const float* __restrict__ bias, int rank, int n, int n_tokens,
+                     float inv_tau) {
   pdl_launch_dependents();
-  extern __shared__ float low[];
-  const size_t t = blockIdx.x;
+  extern __shared__ __align__(16) float low[];                // [rank][AF_CD_TOK]
+  const int t0 = blockIdx.y * AF_CD_TOK;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const float b = c < n ? bias[c] : 0.f;
   pdl_wait();
   proj = pdl_fresh(proj);
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) low[r] = proj[t * ld + off_low + r];
+  for (int i = threadIdx.x; i < rank * AF_CD_TOK; i += blockDim.x) {
+    const int tt = i / rank, r = i - tt * rank;
+    low[r * AF_CD_TOK + tt] = t0 + tt < n_tokens ? proj[(size_t)(t0 + tt) * ld + off_low + r] : 0.f;
+  }
   __syncthreads();
-  for (int c = threadIdx.x; c < n; c += blockDim.x) {
-    float z = 0.f;
-    for (int r = 0; r < rank; ++r) z = fmaf(w2t[(size_t)r * n + c], low[r], z);
-    z += bias[c];
-    const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
-    alpha[t * n + c] = expf(ls * inv_tau);
+  if (c >= n) return;
+  float z[AF_CD_TOK];
+#pragma unroll
+  for (int tt = 0; tt < AF_CD_TOK; ++tt) z[tt] = 0.f;
+#pragma unroll 8
+  for (int r = 0; r < rank; ++r) {
+    const float w = w2t[(size_t)r * n + c];
+    const float4* lr = reinterpret_cast<const float4*>(low + r * AF_CD_TOK);
+#pragma unroll
+    for (int q = 0; q < AF_CD_TOK / 4; ++q) {
+      const float4 l = lr[q];
+      z[4 * q] = fmaf(w, l.x, z[4 * q]);
+      z[4 * q + 1] = fmaf(w, l.y, z[4 * q + 1]);
+      z[4 * q + 2] = fmaf(w, l.z, z[4 * q + 2]);
+      z[4 * q + 3] = fmaf(w, l.w, z[4 * q + 3]);
+    }
+  }
+#pragma unroll
+  for (int tt = 0; tt < AF_CD_TOK; ++tt) {
+    if (t0 + tt >= n_tokens) break;
+    const float zz = z[tt] + b;
+    const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));
+    alpha[(size_t)(t0 + tt) * n + c] = expf(ls * inv_tau);
   }
 }
 
 AF_EXPORT int af_channel_decay(float* alpha, const float* proj, long long ld, int off_low, const float* w2t,
                                const float* bias, int rank, int n_tokens, int n, float tau, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  AF_REQUIRE(n_tokens > 0 && n > 0 && rank > 0 && rank <= 8192 && tau > 0.f, "af_channel_decay: bad sizes (rank up to 8192)");
-  const int threads = n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256;
-  af_launch(channel_decay_kernel, dim3(n_tokens), dim3(threads), (size_t)rank * sizeof(float), stream, alpha, proj, ld,
-            off_low, w2t, bias, rank, n, 1.f / tau);
+  AF_REQUIRE(n_tokens > 0 && n > 0 && rank > 0 && rank <= 512 && tau > 0.f, "af_channel_decay: bad sizes (rank up to 512)");
+  const int sms = af_sm_count();
+  if (sms <= 0) return -1;
+  const int token_tiles = (n_tokens + AF_CD_TOK - 1) / AF_CD_TOK;
+  const int threads = (long long)((n + 127) / 128) * token_tiles >= 2 * sms ? 128 : 32;
+  const dim3 grid((n + threads - 1) / threads, token_tiles);
+  AF_REQUIRE(grid.y < 65536, "af_channel_decay: too many tokens for one grid");
+  af_launch(channel_decay_kernel, grid, dim3(threads), (size_t)rank * AF_CD_TOK * sizeof(float), stream, alpha, proj, ld,
+            off_low, w2t, bias, rank, n, n_tokens, 1.f / tau);
   AF_CHECK_LAUNCH("af_channel_decay");
 }

@@ -33,6 +33,8 @@ for Fiferax and one for Gemma-2 of equal width, depth, feed-forward and vocabula
 ``--banitar all|w1024|w2304|w4096|w4096-192`` does the same for Banitar.
 ``--zatasun all|w1024|w2304|w4096`` does the same for Zatasun (attention beside a gated linear recurrence in
 every layer, dense and routed feed-forwards in turn).
+``--tarorax all|w1024|w2304|w4096`` does the same for Tarorax (four residual streams; gated linear attention in
+three layers of four and differential attention in the fourth; dense and routed feed-forwards in turn).
 """
 from __future__ import annotations
 
@@ -563,6 +565,41 @@ def zatasun_points(args) -> None:
     side_by_side(args, args.zatasun, ZATASUN_POINTS, _zatasun_sizes, "zatasun")
 
 
+def _tarorax_sizes(width, layers, heads, kv_heads, dim, attn_heads, attn_kv_heads, attn_dim, attn_vdim, rank, ff,
+                   experts, top, expert_ff, vocab):
+    """A Tarorax model of `layers` layers over four residual streams (gated linear attention, but differential
+    attention in every fourth layer; a dense feed-forward in the even layers, routed experts of one matrix pair in
+    the odd ones), and the Gemma-2 model of the same width, depth, heads, feed-forward and vocabulary."""
+    gla = {"heads": heads, "dim": dim, "vdim": dim, "tau": 16.0, "rank": rank}
+    att = {"heads": attn_heads, "kv_heads": attn_kv_heads, "dim": attn_dim, "vdim": attn_vdim, "conv": 4, "diff": 0.6,
+           "q_temp": {"coef": 0.5, "every": 64}, "scale": attn_dim ** -0.5, "softcap": 50.0}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff},
+           "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": 4, "keep": 3}}}
+    tx = {"architecture": "Tarorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": 4,
+          "layers": [{"type": "attention" if i % 4 == 2 else "gla", "mixer": att if i % 4 == 2 else gla,
+                      "mlp": {"kind": "dense", "ff": ff} if i % 2 == 0 else moe} for i in range(layers)]}
+    gemma = dict(GEMMA2_2B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                 num_key_value_heads=kv_heads, head_dim=dim, intermediate_size=ff, vocab_size=vocab,
+                 sliding_window=4096, query_pre_attn_scalar=dim)
+    return tx, gemma
+
+
+TARORAX_POINTS = {
+    "w1024": dict(width=1024, layers=8, heads=16, kv_heads=4, dim=64, attn_heads=8, attn_kv_heads=2, attn_dim=64,
+                  attn_vdim=128, rank=64, ff=4096, experts=16, top=2, expert_ff=1024, vocab=32000),
+    "w2304": dict(width=2304, layers=8, heads=18, kv_heads=6, dim=128, attn_heads=9, attn_kv_heads=3, attn_dim=128,
+                  attn_vdim=256, rank=96, ff=9216, experts=16, top=2, expert_ff=2304, vocab=32000),
+    "w4096": dict(width=4096, layers=8, heads=32, kv_heads=8, dim=128, attn_heads=16, attn_kv_heads=4, attn_dim=128,
+                  attn_vdim=256, rank=128, ff=14336, experts=32, top=4, expert_ff=2048, vocab=32000),
+}
+
+
+def tarorax_points(args) -> None:
+    """The same figures for Tarorax beside the Gemma-2 model of equal width, depth, heads, feed-forward and
+    vocabulary."""
+    side_by_side(args, args.tarorax, TARORAX_POINTS, _tarorax_sizes, "tarorax")
+
+
 def side_by_side(args, which, points, make, arm_name) -> None:
     """Prefill and decode of a design at the named points, each beside the Gemma-2 model that `make` pairs it
     with.  One JSON line a model."""
@@ -685,6 +722,8 @@ def main() -> int:
                     help="the same for Banitar (not the default run)")
     ap.add_argument("--zatasun", default="", choices=["", "all", *sorted(ZATASUN_POINTS)],
                     help="the same for Zatasun (not the default run)")
+    ap.add_argument("--tarorax", default="", choices=["", "all", *sorted(TARORAX_POINTS)],
+                    help="the same for Tarorax (not the default run)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -705,6 +744,9 @@ def main() -> int:
         return 0
     if args.zatasun:
         zatasun_points(args)
+        return 0
+    if args.tarorax:
+        tarorax_points(args)
         return 0
     line = run_ours(args)
     if line is not None:

@@ -199,8 +199,10 @@ def route(h, W, p, r):
     return ids, w, margin
 
 
-def moe_ff(h, W, p, mlp):
-    ids, w, _ = route(h, W, p, mlp["router"])
+def moe_ff(h, W, p, mlp, margins=None):
+    ids, w, margin = route(h, W, p, mlp["router"])
+    if margins is not None:
+        margins.append(margin)
     out = torch.zeros(h.shape[0], W[p + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for j in range(ids.shape[1]):
@@ -211,9 +213,10 @@ def moe_ff(h, W, p, mlp):
 
 # ---------------------------------------------------------------- the model
 
-def forward(cfg, W, tokens, layers_out=None, round_h=None):
+def forward(cfg, W, tokens, layers_out=None, round_h=None, margins=None):
     """Logits [T, vocab] of one sequence.  ``layers_out`` (a list) receives the sum of the streams after every
-    layer.  ``round_h``: a function applied to every sublayer's input (to model a 16-bit product input)."""
+    layer, ``margins`` (a list) every router's margins [T].  ``round_h``: a function applied to every sublayer's
+    input (to model a 16-bit product input)."""
     eps = float(cfg["norm"]["eps"])
     rh = round_h or (lambda z: z)
     x = W["embed"][torch.tensor(tokens, dtype=torch.long)]
@@ -227,7 +230,7 @@ def forward(cfg, W, tokens, layers_out=None, round_h=None):
         if layer.get("mlp") is not None:
             mlp = layer["mlp"]
             subs.append((2, lambda h: dense_ff(h, W, p + "mlp.") if mlp["kind"] == "dense"
-                         else moe_ff(h, W, p + "mlp.", mlp)))
+                         else moe_ff(h, W, p + "mlp.", mlp, margins)))
         for qn, fn in subs:
             if has_streams:
                 u = streams_read(X, W[f"{p}hc{qn}.in"])
@@ -242,3 +245,24 @@ def forward(cfg, W, tokens, layers_out=None, round_h=None):
             layers_out.append(sum(X))
     x = sum(X)
     return rh(zero_centred_norm(x, W["final.norm"], eps)) @ W["embed"].T
+
+
+def logits(cfg, W, tokens):
+    return forward(cfg, W, tokens)
+
+
+def routing_margins(cfg, W, tokens):
+    """Per position the smallest margin by which any router of the model chose (infinity without routers)."""
+    m = []
+    forward(cfg, W, tokens, margins=m)
+    out = torch.full((len(tokens),), float("inf"), dtype=F64)
+    for x in m:
+        out = torch.minimum(out, x)
+    return out
+
+
+def generate_greedy(cfg, W, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(forward(cfg, W, ids)[-1].argmax()))
+    return ids[len(prompt):]
