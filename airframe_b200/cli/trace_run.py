@@ -56,8 +56,10 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     # least; up to 256 of them, each with a state of its own in every layer that keeps one) may leave all but one row
     # of its last page empty
     live = max(1, min(args.max_tokens, 256))
+    # (no single request holds more than all live requests together: page tables need no more columns than that)
     rt = GpuRuntime.load(args.model, dtype=args.dtype, device=args.device,
-                         max_tokens=args.max_tokens + kernels.PAGE * live, max_context=limit, max_sequences=live)
+                         max_tokens=args.max_tokens + kernels.PAGE * live,
+                         max_context=min(limit, args.max_tokens + kernels.PAGE), max_sequences=live)
     slots: dict = {}
     for line in stdin:
         line = line.strip()

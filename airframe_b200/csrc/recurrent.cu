@@ -717,11 +717,40 @@ AF_EXPORT int af_gated_scan(void* y, int y_dtype, const float* proj, long long l
 // float32 projection rows that begin at off_low (the first factor of a low-rank pair, applied with the other
 // projections), w2t [rank, n] the second factor transposed.  Worked out as exp(log(sigmoid(z)) / tau) with
 // log(sigmoid(z)) = min(z, 0) - log1p(exp(-|z|)): 32-bit throughout, no underflow of the sigmoid on the way.
-// A block owns AF_CD_TOK tokens and a thread a channel (128 a block; 32 while the step is small, so that more
-// blocks stream the matrix): the tokens' low-rank rows lie in shared memory, a value of w2t is read once for all of
-// the block's tokens (eight of them asked for ahead), and a token's sum runs over r in index order whatever else is
-// in the step.
+// The sum over r is taken in AF_CD_SLICES runs of neighbouring r, each from zero, and the runs are added in order:
+// both kernels below do exactly that, so a prompt and a decode step give the same bits.
+//   many tokens: a block owns AF_CD_TOK tokens and 128 channels (a thread a channel); the tokens' low-rank rows lie
+//                in shared memory and a value of w2t is read once for all of the block's tokens;
+//   few tokens:  a block owns 32 channels, and a warp a run of r: every thread has only rank / AF_CD_SLICES loads
+//                behind one another, and eight times as many warps stream the matrix.
 #define AF_CD_TOK 16
+#define AF_CD_SLICES 8
+
+__device__ __forceinline__ float decay_of(float z, float inv_tau) {
+  const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+  return expf(ls * inv_tau);
+}
+
+// z[.] += w2t[r][c] * low[r][.] for r in [r0, r1): the partial sum of one run, from zero
+__device__ __forceinline__ void decay_run(float* p, const float* __restrict__ w2t, const float* low, int r0, int r1, int n,
+                                          int c) {
+#pragma unroll
+  for (int tt = 0; tt < AF_CD_TOK; ++tt) p[tt] = 0.f;
+#pragma unroll 8
+  for (int r = r0; r < r1; ++r) {
+    const float w = w2t[(size_t)r * n + c];
+    const float4* lr = reinterpret_cast<const float4*>(low + r * AF_CD_TOK);
+#pragma unroll
+    for (int q = 0; q < AF_CD_TOK / 4; ++q) {
+      const float4 l = lr[q];
+      p[4 * q] = fmaf(w, l.x, p[4 * q]);
+      p[4 * q + 1] = fmaf(w, l.y, p[4 * q + 1]);
+      p[4 * q + 2] = fmaf(w, l.z, p[4 * q + 2]);
+      p[4 * q + 3] = fmaf(w, l.w, p[4 * q + 3]);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(128)
 channel_decay_kernel(float* __restrict__ alpha, const float* __restrict__ proj, long long ld, int off_low,
                      const float* __restrict__ w2t, const float* __restrict__ bias, int rank, int n, int n_tokens,
@@ -729,38 +758,63 @@ channel_decay_kernel(float* __restrict__ alpha, const float* __restrict__ proj, 
   pdl_launch_dependents();
   extern __shared__ __align__(16) float low[];                // [rank][AF_CD_TOK]
   const int t0 = blockIdx.y * AF_CD_TOK;
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = blockIdx.x * 128 + threadIdx.x;
   const float b = c < n ? bias[c] : 0.f;
   pdl_wait();
   proj = pdl_fresh(proj);
-  for (int i = threadIdx.x; i < rank * AF_CD_TOK; i += blockDim.x) {
+  for (int i = threadIdx.x; i < rank * AF_CD_TOK; i += 128) {
     const int tt = i / rank, r = i - tt * rank;
     low[r * AF_CD_TOK + tt] = t0 + tt < n_tokens ? proj[(size_t)(t0 + tt) * ld + off_low + r] : 0.f;
   }
   __syncthreads();
   if (c >= n) return;
+  const int per = (rank + AF_CD_SLICES - 1) / AF_CD_SLICES;
   float z[AF_CD_TOK];
 #pragma unroll
   for (int tt = 0; tt < AF_CD_TOK; ++tt) z[tt] = 0.f;
-#pragma unroll 8
-  for (int r = 0; r < rank; ++r) {
-    const float w = w2t[(size_t)r * n + c];
-    const float4* lr = reinterpret_cast<const float4*>(low + r * AF_CD_TOK);
+  for (int s = 0; s < AF_CD_SLICES; ++s) {
+    float p[AF_CD_TOK];
+    decay_run(p, w2t, low, min(s * per, rank), min((s + 1) * per, rank), n, c);
 #pragma unroll
-    for (int q = 0; q < AF_CD_TOK / 4; ++q) {
-      const float4 l = lr[q];
-      z[4 * q] = fmaf(w, l.x, z[4 * q]);
-      z[4 * q + 1] = fmaf(w, l.y, z[4 * q + 1]);
-      z[4 * q + 2] = fmaf(w, l.z, z[4 * q + 2]);
-      z[4 * q + 3] = fmaf(w, l.w, z[4 * q + 3]);
-    }
+    for (int tt = 0; tt < AF_CD_TOK; ++tt) z[tt] += p[tt];
   }
 #pragma unroll
   for (int tt = 0; tt < AF_CD_TOK; ++tt) {
     if (t0 + tt >= n_tokens) break;
-    const float zz = z[tt] + b;
-    const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));
-    alpha[(size_t)(t0 + tt) * n + c] = expf(ls * inv_tau);
+    alpha[(size_t)(t0 + tt) * n + c] = decay_of(z[tt] + b, inv_tau);
+  }
+}
+
+// Up to AF_CD_TOK tokens: block = 32 channels x AF_CD_SLICES runs (warp s takes run s).
+__global__ void __launch_bounds__(32 * AF_CD_SLICES)
+channel_decay_few_kernel(float* __restrict__ alpha, const float* __restrict__ proj, long long ld, int off_low,
+                         const float* __restrict__ w2t, const float* __restrict__ bias, int rank, int n, int n_tokens,
+                         float inv_tau) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) float low[];                // [rank][AF_CD_TOK], then the runs' sums [runs][tokens][32]
+  float* sums = low + (size_t)rank * AF_CD_TOK;
+  const int lane = threadIdx.x & 31, s = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  const float b = c < n ? bias[c] : 0.f;
+  pdl_wait();
+  proj = pdl_fresh(proj);
+  for (int i = threadIdx.x; i < rank * AF_CD_TOK; i += blockDim.x) {
+    const int tt = i / rank, r = i - tt * rank;
+    low[r * AF_CD_TOK + tt] = tt < n_tokens ? proj[(size_t)tt * ld + off_low + r] : 0.f;
+  }
+  __syncthreads();
+  const int per = (rank + AF_CD_SLICES - 1) / AF_CD_SLICES;
+  float p[AF_CD_TOK];
+  decay_run(p, w2t, low, min(s * per, rank), min((s + 1) * per, rank), n, c < n ? c : 0);
+#pragma unroll
+  for (int tt = 0; tt < AF_CD_TOK; ++tt) sums[(s * AF_CD_TOK + tt) * 32 + lane] = p[tt];
+  __syncthreads();
+  if (c >= n) return;
+  for (int tt = s; tt < n_tokens; tt += AF_CD_SLICES) {       // warp s finishes tokens s, s + runs, ...
+    float z = 0.f;
+#pragma unroll
+    for (int q = 0; q < AF_CD_SLICES; ++q) z += sums[(q * AF_CD_TOK + tt) * 32 + lane];
+    alpha[(size_t)tt * n + c] = decay_of(z + b, inv_tau);
   }
 }
 
@@ -768,13 +822,15 @@ AF_EXPORT int af_channel_decay(float* alpha, const float* proj, long long ld, in
                                const float* bias, int rank, int n_tokens, int n, float tau, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   AF_REQUIRE(n_tokens > 0 && n > 0 && rank > 0 && rank <= 512 && tau > 0.f, "af_channel_decay: bad sizes (rank up to 512)");
-  const int sms = af_sm_count();
-  if (sms <= 0) return -1;
-  const int token_tiles = (n_tokens + AF_CD_TOK - 1) / AF_CD_TOK;
-  const int threads = (long long)((n + 127) / 128) * token_tiles >= 2 * sms ? 128 : 32;
-  const dim3 grid((n + threads - 1) / threads, token_tiles);
+  if (n_tokens <= AF_CD_TOK) {
+    const size_t smem = ((size_t)rank * AF_CD_TOK + AF_CD_SLICES * AF_CD_TOK * 32) * sizeof(float);
+    af_launch(channel_decay_few_kernel, dim3((n + 31) / 32), dim3(32 * AF_CD_SLICES), smem, stream, alpha, proj, ld, off_low,
+              w2t, bias, rank, n, n_tokens, 1.f / tau);
+    AF_CHECK_LAUNCH("af_channel_decay");
+  }
+  const dim3 grid((n + 127) / 128, (n_tokens + AF_CD_TOK - 1) / AF_CD_TOK);
   AF_REQUIRE(grid.y < 65536, "af_channel_decay: too many tokens for one grid");
-  af_launch(channel_decay_kernel, grid, dim3(threads), (size_t)rank * AF_CD_TOK * sizeof(float), stream, alpha, proj, ld,
+  af_launch(channel_decay_kernel, grid, dim3(128), (size_t)rank * AF_CD_TOK * sizeof(float), stream, alpha, proj, ld,
             off_low, w2t, bias, rank, n, n_tokens, 1.f / tau);
   AF_CHECK_LAUNCH("af_channel_decay");
 }

@@ -94,7 +94,7 @@ def test_streams_read_and_rewrite(K, S, W, T, out_dtype):
 
 # ---------------------------------------------------------------- gated linear attention
 
-@pytest.mark.parametrize("n,rank,T,tau", [(24, 5, 1, 4.0), (128, 16, 17, 16.0), (130, 1, 40, 1.0), (300, 33, 3, 2.5)])
+@pytest.mark.parametrize("n,rank,T,tau", [(24, 5, 1, 4.0), (128, 16, 17, 16.0), (130, 1, 40, 1.0), (300, 33, 3, 2.5), (256, 128, 50, 16.0)])
 def test_decay_per_key_channel(K, n, rank, T, tau):
     g = torch.Generator().manual_seed(n)
     proj = torch.randn(T, 7 + rank + 3, generator=g) * 3
@@ -104,6 +104,11 @@ def test_decay_per_key_channel(K, n, rank, T, tau):
     K.channel_decay(alpha, proj.to(DEV), 7, w2.t().contiguous().to(DEV), b.to(DEV), tau)
     z = proj[:, 7:7 + rank].double() @ w2.double().T + b.double()
     close(alpha, torch.exp(torch.log(plain.sigmoid(z)) / tau), 1e-5)
+    # a token's decays do not depend on how many tokens the step holds (the kernel for few tokens adds in the same order)
+    for t0, cnt in ((0, 1), (T - 1, 1), (0, min(T, 16)), (max(0, T - 5), min(T, 5))):
+        part = torch.empty(cnt, n, device=DEV)
+        K.channel_decay(part, proj[t0:t0 + cnt].contiguous().to(DEV), 7, w2.t().contiguous().to(DEV), b.to(DEV), tau)
+        assert torch.equal(part, alpha[t0:t0 + cnt])
     # far down the sigmoid's tail the logarithm is taken without the sigmoid underflowing
     deep = torch.full((1, 7 + rank + 3), 0.0)
     K.channel_decay(alpha[:1], deep.to(DEV), 7, w2.t().contiguous().to(DEV), torch.full((n,), -200.0, device=DEV), 100.0)
