@@ -88,10 +88,10 @@ PRESETS["zatasun-small"] = _zatasun_small()
 def _tarorax_small() -> dict:
     """Tarorax with four layers over four streams, the third of them differential attention; dense and routed
     feed-forwards in turn (sizes of no released model)."""
-    gla = {"heads": 8, "dim": 64, "vdim": 64, "tau": 16.0, "rank": 32}
-    att = {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 128, "conv": 4, "diff": 0.6, "scale": 0.125, "softcap": 50.0,
-           "q_temp": {"coef": 0.5, "every": 64}}
-    moe = {"kind": "moe", "expert": {"ff": 256}, "router": {"experts": 8, "top": 2, "scale": 2.0,
+    gla = {"heads": 8, "dim": 64, "vdim": 64, "tau": 8.0, "rank": 32}
+    att = {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 128, "conv": 4, "diff": 0.5, "scale": 0.125, "softcap": 30.0,
+           "q_temp": {"coef": 0.3, "every": 128}}
+    moe = {"kind": "moe", "expert": {"ff": 256}, "router": {"experts": 8, "top": 2, "scale": 2.5,
                                                             "groups": {"count": 4, "keep": 2}}}
     layers = [{"type": "attention" if i == 2 else "gla", "mixer": att if i == 2 else gla,
                "mlp": {"kind": "dense", "ff": 1536} if i % 2 == 0 else moe} for i in range(4)]

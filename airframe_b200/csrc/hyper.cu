@@ -104,8 +104,10 @@ hc_read_kernel(TY* __restrict__ y, const float* __restrict__ x, const float* __r
 }
 
 // x[t][.] rewritten from the sublayer's result; with y: the next sublayer's norm(sum_s in_next[s] x'[t][s]) (offset + w_next)
-template <typename TY, int VEC>
-__global__ void __launch_bounds__(640)
+// SMAX: the streams a thread has registers for (2, 4 or 8: the smallest that holds S; with up to four streams two
+// blocks share an SM, so that one block's loads run under another's reduction).
+template <typename TY, int VEC, int SMAX>
+__global__ void __launch_bounds__(SMAX <= 4 ? 512 : 640, SMAX <= 4 ? 2 : 1)
 hc_write_kernel(float* __restrict__ x, AfHcTerm a, AfHcTerm b, size_t part_stride, const float* __restrict__ ls,
                 const float* __restrict__ mix, const float* __restrict__ out_w, const float* __restrict__ in_next,
                 const float* __restrict__ w_next, float eps, float offset, TY* __restrict__ y, int S, int W) {
@@ -138,21 +140,21 @@ hc_write_kernel(float* __restrict__ x, AfHcTerm a, AfHcTerm b, size_t part_strid
 #pragma unroll
       for (int e = 0; e < VEC; ++e) yv[e] *= l[e];
     }
-    float xs[AF_HC_MAX][VEC];
+    float xs[SMAX][VEC];
 #pragma unroll
-    for (int s = 0; s < AF_HC_MAX; ++s)
+    for (int s = 0; s < SMAX; ++s)
       if (s < S) hc_load<VEC>(xs[s], xt + (size_t)s * W + i);
     float u[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) u[e] = 0.f;
 #pragma unroll
-    for (int to = 0; to < AF_HC_MAX; ++to) {
+    for (int to = 0; to < SMAX; ++to) {
       if (to >= S) continue;
       float nv[VEC];
 #pragma unroll
       for (int e = 0; e < VEC; ++e) nv[e] = 0.f;
 #pragma unroll
-      for (int s = 0; s < AF_HC_MAX; ++s) {
+      for (int s = 0; s < SMAX; ++s) {
         if (s >= S) continue;
         const float c = cmix[s * S + to];
 #pragma unroll
@@ -202,14 +204,13 @@ stream_sum_kernel(float* __restrict__ out, const float* __restrict__ x, int S, i
   }
 }
 
-// Threads of a token's block: as many as give every thread the same number of channel groups, up to 640 (a row of
-// up to 2560 values is then one group of four a thread, all its loads in flight at once).
-static int hc_threads(int W, int vec, int n_tokens) {
-  (void)n_tokens;
+// Threads of a token's block: as many as give every thread the same number of channel groups, up to `most` (all loads of a
+// thread's groups are in flight at once).
+static int hc_threads(int W, int vec, int most = 640) {
   const int groups = (W + vec - 1) / vec;
-  const int iters = (groups + 639) / 640;
+  const int iters = (groups + most - 1) / most;
   int th = (((groups + iters - 1) / iters + 31) / 32) * 32;
-  return th < 32 ? 32 : th > 640 ? 640 : th;
+  return th < 32 ? 32 : th > most ? most : th;
 }
 
 AF_EXPORT int af_hc_read(void* y, int y_dtype, const float* x, const float* in_w, const float* w, float eps, float offset,
@@ -220,10 +221,10 @@ AF_EXPORT int af_hc_read(void* y, int y_dtype, const float* x, const float* in_w
   const bool vec = W % 4 == 0 && ((uintptr_t)x & 15) == 0;
   const size_t smem = (size_t)W * sizeof(float);
   if (vec) {
-    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_read_kernel<TY, 4>, dim3(n_tokens), dim3(hc_threads(W, 4, n_tokens)), smem, stream,
+    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_read_kernel<TY, 4>, dim3(n_tokens), dim3(hc_threads(W, 4)), smem, stream,
                                              (TY*)y, x, in_w, w, eps, offset, S, W));
   } else {
-    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_read_kernel<TY, 1>, dim3(n_tokens), dim3(hc_threads(W, 1, n_tokens)), smem, stream,
+    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_read_kernel<TY, 1>, dim3(n_tokens), dim3(hc_threads(W, 1)), smem, stream,
                                              (TY*)y, x, in_w, w, eps, offset, S, W));
   }
   AF_CHECK_LAUNCH("af_hc_read");
@@ -247,13 +248,23 @@ AF_EXPORT int af_hc_write(float* x, const void* a, int a_dtype, int a_parts, flo
   const size_t part_stride = (size_t)n_tokens * W;
   const bool vec = W % 4 == 0 && (((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)ls) & 15) == 0;
   const size_t smem = y != nullptr ? (size_t)W * sizeof(float) : 0;
+#define AF_HC_LAUNCH(VEC_, SMAX_)                                                                                      \
+  AF_DISPATCH_DTYPE(y_dtype, TY,                                                                                       \
+                    af_launch(hc_write_kernel<TY, VEC_, SMAX_>, dim3(n_tokens), dim3(hc_threads(W, VEC_, SMAX_ <= 4 ? 512 : 640)), smem, \
+                              stream, x, ta, tb, part_stride, ls, mix, out_w, in_next, w_next, eps, offset, (TY*)y, S, W))
+  // few tokens (a decode step): the variant with registers for eight streams, whose blocks may be wide enough to
+  // have all of a row's loads in flight at once; many tokens: the smallest that holds S, two blocks an SM
+  const bool few = n_tokens < 512;
   if (vec) {
-    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_write_kernel<TY, 4>, dim3(n_tokens), dim3(hc_threads(W, 4, n_tokens)), smem, stream, x,
-                                             ta, tb, part_stride, ls, mix, out_w, in_next, w_next, eps, offset, (TY*)y, S, W));
+    if (S <= 2 && !few) AF_HC_LAUNCH(4, 2);
+    else if (S <= 4 && !few) AF_HC_LAUNCH(4, 4);
+    else AF_HC_LAUNCH(4, 8);
   } else {
-    AF_DISPATCH_DTYPE(y_dtype, TY, af_launch(hc_write_kernel<TY, 1>, dim3(n_tokens), dim3(hc_threads(W, 1, n_tokens)), smem, stream, x,
-                                             ta, tb, part_stride, ls, mix, out_w, in_next, w_next, eps, offset, (TY*)y, S, W));
+    if (S <= 2 && !few) AF_HC_LAUNCH(1, 2);
+    else if (S <= 4 && !few) AF_HC_LAUNCH(1, 4);
+    else AF_HC_LAUNCH(1, 8);
   }
+#undef AF_HC_LAUNCH
   AF_CHECK_LAUNCH("af_hc_write");
 }
 

@@ -570,11 +570,11 @@ def _tarorax_sizes(width, layers, heads, kv_heads, dim, attn_heads, attn_kv_head
     """A Tarorax model of `layers` layers over four residual streams (gated linear attention, but differential
     attention in every fourth layer; a dense feed-forward in the even layers, routed experts of one matrix pair in
     the odd ones), and the Gemma-2 model of the same width, depth, heads, feed-forward and vocabulary."""
-    gla = {"heads": heads, "dim": dim, "vdim": dim, "tau": 16.0, "rank": rank}
-    att = {"heads": attn_heads, "kv_heads": attn_kv_heads, "dim": attn_dim, "vdim": attn_vdim, "conv": 4, "diff": 0.6,
-           "q_temp": {"coef": 0.5, "every": 64}, "scale": attn_dim ** -0.5, "softcap": 50.0}
+    gla = {"heads": heads, "dim": dim, "vdim": dim, "tau": 8.0, "rank": rank}
+    att = {"heads": attn_heads, "kv_heads": attn_kv_heads, "dim": attn_dim, "vdim": attn_vdim, "conv": 4, "diff": 0.5,
+           "q_temp": {"coef": 0.3, "every": 128}, "scale": attn_dim ** -0.5, "softcap": 30.0}
     moe = {"kind": "moe", "expert": {"ff": expert_ff},
-           "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": 4, "keep": 3}}}
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
     tx = {"architecture": "Tarorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": 4,
           "layers": [{"type": "attention" if i % 4 == 2 else "gla", "mixer": att if i % 4 == 2 else gla,
                       "mlp": {"kind": "dense", "ff": ff} if i % 2 == 0 else moe} for i in range(layers)]}

@@ -53,8 +53,8 @@ TA = {
 TB = {
     "architecture": "Tarorax", "vocab": 320, "width": 128, "norm": {"eps": 1e-6}, "streams": 4,
     "layers": [
-        _layer("gla", _gla(2, 64, 64, 16.0, 16), _dense(256)),
-        _layer("attention", _att(4, 2, 64, 64, 0.125, 0.6, conv=4, softcap=50.0, q_temp=(0.5, 64)), _moe(8, 4, 64, 2.0, (4, 3))),
+        _layer("gla", _gla(2, 64, 64, 12.0, 16), _dense(256)),
+        _layer("attention", _att(4, 2, 64, 64, 0.125, 0.55, conv=4, softcap=40.0, q_temp=(0.4, 48)), _moe(8, 4, 64, 1.75, (4, 3))),
         _layer("gla", _gla(1, 128, 128, 2.0, 8), _moe(8, 2, 96, 2.5, (2, 2))),
         _layer("attention", _att(2, 1, 128, 128, 0.09, 0.3, conv=4, softcap=20.0, q_temp=(1.0, 32)), _dense(192)),
         _layer("attention", _att(2, 2, 32, 64, 0.2, 0.5, conv=2, q_temp=(0.5, 3))),
