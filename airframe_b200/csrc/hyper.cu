@@ -10,7 +10,7 @@
 // All sums are 32-bit.  One block per token; a thread owns groups of VEC neighbouring channels.
 #include "common.cuh"
 
-#define AF_HC_MAX 8
+#define AF_HC_MAX 16
 
 struct AfHcTerm {
   const void* p;
@@ -104,10 +104,10 @@ hc_read_kernel(TY* __restrict__ y, const float* __restrict__ x, const float* __r
 }
 
 // x[t][.] rewritten from the sublayer's result; with y: the next sublayer's norm(sum_s in_next[s] x'[t][s]) (offset + w_next)
-// SMAX: the streams a thread has registers for (2, 4 or 8: the smallest that holds S; with up to four streams two
-// blocks share an SM, so that one block's loads run under another's reduction).
+// SMAX: the streams a thread has registers for (2, 4, 8 or 16: the smallest that holds S; with up to four streams two
+// blocks share an SM, so that one block's loads run under another's reduction; sixteen want narrow blocks).
 template <typename TY, int VEC, int SMAX>
-__global__ void __launch_bounds__(SMAX <= 4 ? 512 : 640, SMAX <= 4 ? 2 : 1)
+__global__ void __launch_bounds__(SMAX <= 4 ? 512 : SMAX <= 8 ? 640 : 256, SMAX <= 4 ? 2 : 1)
 hc_write_kernel(float* __restrict__ x, AfHcTerm a, AfHcTerm b, size_t part_stride, const float* __restrict__ ls,
                 const float* __restrict__ mix, const float* __restrict__ out_w, const float* __restrict__ in_next,
                 const float* __restrict__ w_next, float eps, float offset, TY* __restrict__ y, int S, int W) {
@@ -250,7 +250,7 @@ AF_EXPORT int af_hc_write(float* x, const void* a, int a_dtype, int a_parts, flo
   const size_t smem = y != nullptr ? (size_t)W * sizeof(float) : 0;
 #define AF_HC_LAUNCH(VEC_, SMAX_)                                                                                      \
   AF_DISPATCH_DTYPE(y_dtype, TY,                                                                                       \
-                    af_launch(hc_write_kernel<TY, VEC_, SMAX_>, dim3(n_tokens), dim3(hc_threads(W, VEC_, SMAX_ <= 4 ? 512 : 640)), smem, \
+                    af_launch(hc_write_kernel<TY, VEC_, SMAX_>, dim3(n_tokens), dim3(hc_threads(W, VEC_, SMAX_ <= 4 ? 512 : SMAX_ <= 8 ? 640 : 256)), smem, \
                               stream, x, ta, tb, part_stride, ls, mix, out_w, in_next, w_next, eps, offset, (TY*)y, S, W))
   // few tokens (a decode step): the variant with registers for eight streams, whose blocks may be wide enough to
   // have all of a row's loads in flight at once; many tokens: the smallest that holds S, two blocks an SM
@@ -258,11 +258,13 @@ AF_EXPORT int af_hc_write(float* x, const void* a, int a_dtype, int a_parts, flo
   if (vec) {
     if (S <= 2 && !few) AF_HC_LAUNCH(4, 2);
     else if (S <= 4 && !few) AF_HC_LAUNCH(4, 4);
-    else AF_HC_LAUNCH(4, 8);
+    else if (S <= 8) AF_HC_LAUNCH(4, 8);
+    else AF_HC_LAUNCH(4, 16);
   } else {
     if (S <= 2 && !few) AF_HC_LAUNCH(1, 2);
     else if (S <= 4 && !few) AF_HC_LAUNCH(1, 4);
-    else AF_HC_LAUNCH(1, 8);
+    else if (S <= 8) AF_HC_LAUNCH(1, 8);
+    else AF_HC_LAUNCH(1, 16);
   }
 #undef AF_HC_LAUNCH
   AF_CHECK_LAUNCH("af_hc_write");

@@ -1456,7 +1456,7 @@ def expert_rows_tc(out, a, w0, w1=None, perm=None, plan=None, pair_weight=None, 
 
 # ---------------------------------------------------------------- a residual stream in several copies
 
-HC_MAX_STREAMS = 8
+HC_MAX_STREAMS = 16
 
 
 def _hc_stream(x, S: int, W: int, who: str):

@@ -80,7 +80,7 @@ def test_config_refuses_what_it_does_not_know():
     broken(lambda d: d.update(layers=[]))
     from airframe_b200.engine.model import declared_weights
     with pytest.raises(ConfigError):          # more streams than the kernels keep in registers: refused when the model is put together
-        declared_weights(config_from_dict(dict(copy.deepcopy(TA), streams=9)).model_spec())
+        declared_weights(config_from_dict(dict(copy.deepcopy(TA), streams=17)).model_spec())
 
 
 def test_declared_tensors():

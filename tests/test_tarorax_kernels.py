@@ -50,7 +50,7 @@ def batch_of(lens, slots, before=None):
 
 # ---------------------------------------------------------------- the streams
 
-@pytest.mark.parametrize("S,W,T", [(1, 50, 3), (3, 72, 9), (4, 128, 40), (8, 36, 5), (2, 2052, 2)])
+@pytest.mark.parametrize("S,W,T", [(1, 50, 3), (3, 72, 9), (4, 128, 40), (8, 36, 5), (2, 2052, 2), (11, 64, 600), (16, 130, 4)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_streams_read_and_rewrite(K, S, W, T, out_dtype):
     g = torch.Generator().manual_seed(S * 1000 + W)
