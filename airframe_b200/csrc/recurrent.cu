@@ -834,3 +834,127 @@ AF_EXPORT int af_channel_decay(float* alpha, const float* proj, long long ld, in
             off_low, w2t, bias, rank, n, n_tokens, 1.f / tau);
   AF_CHECK_LAUNCH("af_channel_decay");
 }
+
+// ---------------------------------------------------------------- a long prompt's scan, chunks side by side
+
+// The recurrence S <- diag(w_t) S + k_t v_t^T is linear in S, so a sequence can be cut into chunks that are scanned
+// side by side, each from a zero state (state_scan over the chunks as if they were sequences: that gives
+// o_local_t = S_local_t^T q_t and every chunk's final local state B), and joined afterwards, all in 32 bits:
+//   cumulate   A_t = prod of w_s over the chunk's tokens s <= t                       (per key channel)
+//   carry      S_in(first chunk) = the sequence's cached state; S_in(c + 1) = diag(A_end(c)) S_in(c) + B(c);
+//              the last one is the sequence's new cached state
+//   correct    o_t = o_local_t + S_in(chunk of t)^T (q_t * A_t)
+// No quotient of decays is taken anywhere, so a channel that forgets quickly only drives its A towards zero.
+// plan (int32, made on the host once a step): chunk_starts [n_chunks + 1] rows; seq_first_chunk [n_seqs + 1];
+// tiles [n_tiles][3] = (first row, rows (<= 32), chunk).
+
+__global__ void __launch_bounds__(128)
+chunk_cumulate_kernel(float* __restrict__ A, const float* __restrict__ w, long long w_ts, const int* __restrict__ chunk_starts,
+                      int n) {
+  pdl_launch_dependents();
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  const int first = chunk_starts[blockIdx.y], last = chunk_starts[blockIdx.y + 1];
+  pdl_wait();
+  if (c >= n) return;
+  float p = 1.f;
+#pragma unroll 8
+  for (int t = first; t < last; ++t) {
+    p *= w[(size_t)t * w_ts + c];
+    A[(size_t)t * n + c] = p;
+  }
+}
+
+// One thread a state element (head, value column, key channel); blockIdx.y = sequence.  `local` holds B(c) on entry
+// and S_in(c) on exit.
+__global__ void __launch_bounds__(256)
+chunk_carry_kernel(float* __restrict__ local, float* __restrict__ state, const float* __restrict__ A,
+                   const int* __restrict__ chunk_starts, const int* __restrict__ seq_first_chunk,
+                   const int* __restrict__ slots, int heads, int dk, int dv) {
+  pdl_launch_dependents();
+  const size_t per = (size_t)heads * dv * dk;
+  const size_t e = (size_t)blockIdx.x * 256 + threadIdx.x;
+  const int b = blockIdx.y;
+  const int slot = slots[b];
+  const int c0 = seq_first_chunk[b], c1 = seq_first_chunk[b + 1];
+  pdl_wait();
+  if (e >= per || slot < 0) return;
+  const int ch = (int)(e % dk);
+  const int h = (int)(e / ((size_t)dv * dk));
+  const int n = heads * dk;
+  float S = state[(size_t)slot * per + e];
+  for (int c = c0; c < c1; ++c) {
+    const float B = local[(size_t)c * per + e];
+    const float a = A[(size_t)(chunk_starts[c + 1] - 1) * n + h * dk + ch];
+    local[(size_t)c * per + e] = S;
+    S = fmaf(a, S, B);
+  }
+  state[(size_t)slot * per + e] = S;
+}
+
+// Block (x, y, z) = (32 value columns, head, tile of up to 32 tokens of one chunk); 256 threads: thread (j, r) owns
+// column j of tokens r, r + 8, r + 16, r + 24.  The key channels go through shared memory 64 at a time.
+__global__ void __launch_bounds__(256)
+chunk_correct_kernel(float* __restrict__ out, long long out_ts, const float* __restrict__ q, long long q_ts,
+                     const float* __restrict__ A, const float* __restrict__ s_in, const int* __restrict__ tiles, int heads,
+                     int dk, int dv) {
+  pdl_launch_dependents();
+  __shared__ float Ss[32][65];
+  __shared__ float Qs[32][64];
+  const int j = threadIdx.x & 31, r = threadIdx.x >> 5;
+  const int j0 = blockIdx.x * 32, h = blockIdx.y;
+  const int row0 = tiles[3 * blockIdx.z], rows = tiles[3 * blockIdx.z + 1], chunk = tiles[3 * blockIdx.z + 2];
+  const int n = heads * dk;
+  const float* S = s_in + (((size_t)chunk * heads + h) * dv) * dk;
+  pdl_wait();
+  q = pdl_fresh(q);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int c0 = 0; c0 < dk; c0 += 64) {
+    for (int i = threadIdx.x; i < 32 * 64; i += 256) {
+      const int jj = i >> 6, cc = i & 63;
+      Ss[jj][cc] = (j0 + jj < dv && c0 + cc < dk) ? S[(size_t)(j0 + jj) * dk + c0 + cc] : 0.f;
+      const int tt = jj;                              // (the same index walks the tile's tokens)
+      float v = 0.f;
+      if (tt < rows && c0 + cc < dk) {
+        const size_t t = (size_t)(row0 + tt);
+        v = q[t * q_ts + h * dk + c0 + cc] * A[t * n + h * dk + c0 + cc];
+      }
+      Qs[tt][cc] = v;
+    }
+    __syncthreads();
+#pragma unroll 16
+    for (int cc = 0; cc < 64; ++cc) {
+      const float s = Ss[j][cc];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc[u] = fmaf(s, Qs[r + 8 * u][cc], acc[u]);
+    }
+    __syncthreads();
+  }
+  if (j0 + j >= dv) return;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int tt = r + 8 * u;
+    if (tt < rows) out[(size_t)(row0 + tt) * out_ts + h * dv + j0 + j] += acc[u];
+  }
+}
+
+// After af_state_scan over the chunks (rule CHANNEL, `local` [n_chunks, heads, dv, dk] as its zeroed state): join them.
+// A: scratch [n_tokens, heads * dk].
+AF_EXPORT int af_chunk_join(float* out, long long out_ts, const float* q, long long q_ts, const float* w, long long w_ts,
+                            float* A, float* local, float* state, const int* chunk_starts, const int* seq_first_chunk,
+                            const int* tiles, const int* slots, int n_chunks, int n_seqs, int n_tiles, int heads, int dk,
+                            int dv, cudaStream_t stream) {
+  if (n_chunks == 0) return 0;
+  AF_REQUIRE(n_chunks > 0 && n_seqs > 0 && n_tiles > 0 && heads > 0 && dk > 0 && dv > 0, "af_chunk_join: bad sizes");
+  AF_REQUIRE(n_chunks < 65536 && n_seqs < 65536 && n_tiles < 65536 && heads < 65536,
+             "af_chunk_join: too many chunks, sequences, tiles or heads for one grid");
+  const int n = heads * dk;
+  af_launch(chunk_cumulate_kernel, dim3((n + 127) / 128, n_chunks), dim3(128), 0, stream, A, w, w_ts, chunk_starts, n);
+  AF_COUNT_LAUNCH("af_chunk_join");
+  const size_t per = (size_t)heads * dv * dk;
+  af_launch(chunk_carry_kernel, dim3((unsigned)((per + 255) / 256), n_seqs), dim3(256), 0, stream, local, state,
+            (const float*)A, chunk_starts, seq_first_chunk, slots, heads, dk, dv);
+  AF_COUNT_LAUNCH("af_chunk_join");
+  af_launch(chunk_correct_kernel, dim3((dv + 31) / 32, heads, n_tiles), dim3(256), 0, stream, out, out_ts, q, q_ts,
+            (const float*)A, (const float*)local, tiles, heads, dk, dv);
+  AF_CHECK_LAUNCH("af_chunk_join");
+}

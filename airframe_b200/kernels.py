@@ -1539,6 +1539,62 @@ def channel_decay(alpha, proj, off_low: int, w2t, bias, tau: float) -> None:
                                    _stream()))
 
 
+SCAN_CHUNK = 128     # tokens of a chunk when a long prompt's scan is cut into chunks that run side by side
+
+
+class _ChunkBatch:
+    """What ``state_scan`` reads of a batch, with the chunks of a step standing for its sequences."""
+
+    def __init__(self, seq_starts, slots, n_seqs):
+        self.seq_starts, self.slots, self.n_seqs = seq_starts, slots, n_seqs
+
+
+def _scan_chunks(batch, chunk: int):
+    """The chunks of a prefill step's sequences (made on the host once a step, kept in ``batch.aux``): device
+    tensors chunk_starts [n_chunks + 1], seq_first_chunk [n_seqs + 1], tiles [n_tiles, 3] = (first row, rows <= 32,
+    chunk), the chunks' own slots 0 .. n_chunks - 1, and the counts."""
+    key = ("scan_chunks", chunk)
+    if key not in batch.aux:
+        starts, first, tiles, row = [], [0], [], 0
+        for n in batch.seq_lens:
+            for c0 in range(0, n, chunk):
+                rows = min(chunk, n - c0)
+                for t0 in range(0, rows, 32):
+                    tiles.append((row + c0 + t0, min(32, rows - t0), len(starts)))
+                starts.append(row + c0)
+            row += n
+            first.append(len(starts))
+        starts.append(row)
+        n_chunks = len(starts) - 1
+        flat = starts + first + [x for t in tiles for x in t] + list(range(n_chunks))
+        dev = torch.tensor(flat, dtype=torch.int32).to(batch.tokens.device)
+        a, b, c = len(starts), len(starts) + len(first), len(starts) + len(first) + 3 * len(tiles)
+        batch.aux[key] = (dev[:a], dev[a:b], dev[b:c], dev[c:], n_chunks, len(tiles))
+    return batch.aux[key]
+
+
+def state_scan_chunked(out, r, k, v, w, state, batch, heads: int, dk: int, dv: int, chunk: int = SCAN_CHUNK) -> None:
+    """:func:`state_scan` with the rule ``channel`` for a prefill step of few, long sequences: every sequence is cut
+    into chunks of ``chunk`` tokens that are scanned side by side from zero states, then joined (the decays
+    cumulated within a chunk, the states carried from chunk to chunk, every token's output corrected by what its
+    chunk's entering state adds): the same sums in another order, all in 32 bits."""
+    T = out.shape[0]
+    if tuple(w.shape) != (T, heads * dk):
+        raise KernelError(f"state_scan_chunked: a decay per key channel and token, [{T}, {heads * dk}]")
+    chunk_starts, seq_first, tiles, own_slots, n_chunks, n_tiles = _scan_chunks(batch, chunk)
+    local = torch.zeros(n_chunks, heads, dv, dk, dtype=torch.float32, device=out.device)
+    state_scan("channel", out, r, k, v, local, _ChunkBatch(chunk_starts, own_slots, n_chunks), heads, dk, dv, w=w)
+    A = torch.empty(T, heads * dk, dtype=torch.float32, device=out.device)
+    op, ots = _f32_rows(out, "out")
+    rp, rts = _f32_rows(r, "r")
+    wp, wts = _f32_rows(w, "w")
+    i32 = torch.int32
+    _check(_lib().af_chunk_join(op, ots, rp, rts, wp, wts, _ptr(A), _ptr(local), _ptr(state, "state", torch.float32),
+                                _ptr(chunk_starts, "chunk_starts", i32), _ptr(seq_first, "seq_first", i32),
+                                _ptr(tiles, "tiles", i32), _ptr(batch.slots, "slots", i32), c_int(n_chunks),
+                                c_int(batch.n_seqs), c_int(n_tiles), c_int(heads), c_int(dk), c_int(dv), _stream()))
+
+
 def conv_pack(qkv, proj, batch, H: int, G: int, d: int, dv: int, pk: int, pv: int, bias=None, taps_w=None, history=None,
               temp_coef: float = 0.0, temp_every: int = 0, kv=None) -> None:
     """From float32 projection rows [q (H heads of two maps of d) | k (G heads of two maps) | v (G heads of dv)], plus

@@ -336,7 +336,7 @@ class GatedLinearAttention(_StateMixer):
     Parameters: ``hidden_size``, ``num_heads``, ``head_dim`` (queries and keys), ``value_dim``, ``tau``, ``eps``,
     ``weights``: tensor names for ``q, k, v, g, a1, a2, a2_bias, norm, o``; optional ``query_scale`` (default
     head_dim^-1/2), ``decay_rank`` (rows of a1; read from the tensor when absent), ``gate`` ("silu", the default, or
-    "sigmoid")."""
+    "sigmoid"), ``chunked_scan`` (default true: a step of few long prompts scans chunks of them side by side)."""
     ROLES = ("q", "k", "v", "g", "a1", "a2", "a2_bias", "norm", "o")
 
     def __init__(self, params, ctx):
@@ -387,6 +387,24 @@ class GatedLinearAttention(_StateMixer):
         T = sum(lens)
         return 2 * T * (self.w_in.numel() + self.w_o.numel() + self.w2t.numel()) + T * self.heads * 5 * self.dk * self.dv
 
+    def _chunk(self, batch) -> int:
+        """Tokens of a chunk for this prefill step's scan, or 0: the sequences as they are.  The token-by-token scan
+        has a block a (sequence, head, 32 value columns); while those leave half the SMs without one, the sequences
+        are cut into so many chunks that there are about four blocks an SM, of at least ``kernels.SCAN_CHUNK`` tokens
+        (a power of two of them), if that leaves the longest sequence two chunks at least.  (With a block an SM the
+        scan already runs near what an SM does with four: chunks then only add the join; measured at 32 heads of 128.)"""
+        if not bool(self.params.get("chunked_scan", True)):
+            return 0
+        sms = kernels.sm_count()
+        blocks = batch.n_seqs * self.heads * -(-self.dv // 32)
+        if 2 * blocks > sms:
+            return 0
+        want = -(-4 * sms // blocks)
+        chunk = kernels.SCAN_CHUNK
+        while chunk * want < batch.max_len and chunk < 4096:
+            chunk *= 2
+        return chunk if batch.max_len >= 2 * chunk else 0
+
     def forward(self, x, batch, view):
         T, off, f32 = x.shape[0], self.off, torch.float32
         nk, nv = self.heads * self.dk, self.heads * self.dv
@@ -394,8 +412,14 @@ class GatedLinearAttention(_StateMixer):
         alpha = torch.empty(T, nk, dtype=f32, device=x.device)
         kernels.channel_decay(alpha, proj, off["a1"], self.w2t, self.a2_bias, self.tau)
         o = torch.empty(T, nv, dtype=f32, device=x.device)
-        kernels.state_scan("channel", o, proj[:, off["q"]: off["q"] + nk], proj[:, off["k"]: off["k"] + nk],
-                           proj[:, off["v"]: off["v"] + nv], view.state, batch, self.heads, self.dk, self.dv, w=alpha)
+        q, k, v = (proj[:, off[n]: off[n] + w] for n, w in (("q", nk), ("k", nk), ("v", nv)))
+        # few long prompts: their tokens one after the other leave most of the GPU idle (a block a head and tile of
+        # value columns); cut into chunks that are scanned side by side and joined, the same sums fill it
+        chunk = self._chunk(batch) if batch.is_prefill else 0
+        if chunk:
+            kernels.state_scan_chunked(o, q, k, v, alpha, view.state, batch, self.heads, self.dk, self.dv, chunk=chunk)
+        else:
+            kernels.state_scan("channel", o, q, k, v, view.state, batch, self.heads, self.dk, self.dv, w=alpha)
         y = torch.empty(T, nv, dtype=x.dtype, device=x.device)
         kernels.gated_group_norm(y, o, self.norm_w, proj[:, off["g"]: off["g"] + nv], self.dv, self.eps,
                                  gate_act=self.gate, in_scale=self.query_scale)

@@ -48,6 +48,12 @@ def batch_of(lens, slots, before=None):
                            max_len=max(lens), seq_lens=list(lens), max_len_after=max(after), aux={})
 
 
+def batch_of_aux(lens, slots, some_device_tensor):
+    b = batch_of(lens, slots)
+    b.tokens = some_device_tensor
+    return b
+
+
 # ---------------------------------------------------------------- the streams
 
 @pytest.mark.parametrize("S,W,T", [(1, 50, 3), (3, 72, 9), (4, 128, 40), (8, 36, 5), (2, 2052, 2), (11, 64, 600), (16, 130, 4)])
@@ -153,6 +159,46 @@ def test_scan_with_a_decay_per_channel(K, heads, dk, dv):
         got.append(o[:n])
         at += n
     close(torch.cat(got), ref[0], 2e-5)
+
+
+@pytest.mark.parametrize("heads,dk,dv,lens,chunk", [(2, 8, 8, [300, 1, 130], 128), (3, 24, 40, [257], 64), (1, 64, 100, [64, 65, 200], 64),
+                                                    (2, 128, 128, [520], 128), (1, 5, 3, [33, 70], 32), (2, 70, 33, [129, 2], 128)])
+def test_chunks_scanned_side_by_side_and_joined(K, heads, dk, dv, lens, chunk):
+    """Sequences cut into chunks (a last chunk of one token, of a whole chunk, sequences shorter than a chunk), from
+    states that earlier steps left: outputs and new states against the token-by-token kernel and the plain
+    recurrence; a channel that forgets everything at once inside a chunk, and one that forgets nothing."""
+    T = sum(lens)
+    g = torch.Generator().manual_seed(dk * 7 + dv + T)
+    q, k, v = (torch.randn(T, heads * n, generator=g) for n in (dk, dk, dv))
+    alpha = torch.rand(T, heads * dk, generator=g) * 0.5 + 0.5
+    alpha[:, 0] = 1.0
+    alpha[T // 2, 1 % (heads * dk)] = 0.0
+    alpha[:, -1] = 0.05                      # (its cumulated decay leaves the range of 32-bit floats within a chunk)
+    slots = list(range(1, len(lens) + 1))
+    start = torch.randn(len(lens) + 2, heads, dv, dk, generator=g)
+    dev = [t.to(DEV) for t in (q, k, v, alpha)]
+    b = batch_of(lens, slots)
+    b.tokens = dev[0]
+    want_state = start.clone().to(DEV)
+    want = torch.empty(T, heads * dv, device=DEV)
+    K.state_scan("channel", want, dev[0], dev[1], dev[2], want_state, b, heads, dk, dv, w=dev[3])
+    got_state = start.clone().to(DEV)
+    got = torch.full((T, heads * dv), 7.0, device=DEV)
+    K.state_scan_chunked(got, dev[0], dev[1], dev[2], dev[3], got_state, b, heads, dk, dv, chunk=chunk)
+    close(got, want, 2e-5)
+    close(got_state, want_state, 2e-5)
+    assert torch.equal(got_state[0], start[0].to(DEV)) and torch.equal(got_state[-1], start[-1].to(DEV))
+    # and against the plain recurrence from a zero state
+    zero = torch.zeros_like(got_state)
+    K.state_scan_chunked(got, dev[0], dev[1], dev[2], dev[3], zero, batch_of_aux(lens, slots, dev[0]), heads, dk, dv, chunk=chunk)
+    at = 0
+    for n in lens:
+        s = slice(at, at + n)
+        ref = torch.cat([plain.decayed_outer_product_scan(q[s, h * dk:(h + 1) * dk].double(), k[s, h * dk:(h + 1) * dk].double(),
+                                                          v[s, h * dv:(h + 1) * dv].double(), alpha[s, h * dk:(h + 1) * dk].double())
+                         for h in range(heads)], dim=1)
+        close(got[s], ref, 3e-5)
+        at += n
 
 
 @pytest.mark.parametrize("heads,dv", [(3, 20), (2, 64), (1, 7)])
