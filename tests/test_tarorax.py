@@ -312,6 +312,24 @@ def test_long_decoding_over_pages(dtype, tmp_path_factory):
         agrees(tail, Ref(whole.double(), r.sure, 1.5 * r.noise), dtype, rms=5e-2, worst=0.3)
 
 
+@gpu
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_prompts_whose_scan_is_cut_into_chunks(name, dtype, tmp_path_factory):
+    """Prompts long enough that the linear attention's scan runs as chunks side by side (five and a half chunks; a
+    last chunk of one token): alone, with their last tokens one by one, and two of them beside a short request in
+    one step, against the plain implementation."""
+    c = case(name, tmp_path_factory)
+    rt = load(c, dtype, max_tokens=64 * 40)
+    V = c["cfg"]["vocab"]
+    reqs = [replay.random_ids(V, n, 500 + n) for n in (700, 513, 5)]
+    refs = [reference(c, r) for r in reqs]
+    agrees(replay.run_whole(rt, reqs[0]), refs[0], dtype)
+    agrees(replay.run_tail(rt, reqs[0], 30), refs[0], dtype)
+    out, _ = replay.run_batches(rt, reqs, 3, [690, 513, 3])
+    for i, r in enumerate(refs):
+        agrees(out[i], r, dtype, i)
+
+
 def _loud_first_token(name, t):
     """The embedding of token 0 made large: what the first position leaves in keys, values and states is then seen
     from far away through the norms."""
